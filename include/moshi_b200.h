@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define B200_ABI_VERSION 2
+#define B200_ABI_VERSION 3
 
 enum {
   B200_OK = 0,
@@ -319,6 +319,72 @@ int b200_frame_step(b200_frame* f, const float* pcm_in_host, const int32_t* upda
  * mimi.encode produced and lm_gen.step consumed, server.py:133-138), "tokens" i64 [B,dep_q+1], "codes_out" i64 [B,dep_q] (what
  * mimi.decode consumed), "exec" / "decoder_exec" u8 [B]. */
 int b200_frame_read_buffer(b200_frame* f, const char* name, void* dst_dev, int64_t capacity_bytes, int64_t* nbytes);
+
+/* ------------------------------------------------------------------------------------------ */
+/* Decoder LM: a text-only stack of layers listed by its configuration (no reference counterpart) */
+/* ------------------------------------------------------------------------------------------ */
+/* A decoder-only language model given as a list of layers; every layer names its token mixer and its feed-forward, so
+ * that one handle serves every design built from the registered mechanisms.  Registered so far (the Likosun design):
+ *   block   one layer norm (weight + bias) feeds mixer and feed-forward in parallel; each result is gated element-wise by
+ *           sigmoid(G h + g); X_{i+1} = x + residual_mult * (gated sum); the next layer reads the depth-weighted average
+ *           sum_j a_ij X_j of the embedding output and all layer results so far
+ *   mixer   B200_MIXER_LATENT_ATTENTION: position-free causal attention over a compressed latent c = rmsnorm(W_dkv h) * w
+ *           (keys / values are W_uk c / W_uv c per head), softmax with one learnt sink logit per head in the denominator;
+ *           ONLY c is cached, the kernels score against it directly (W_uk folded into the query, W_uv applied after the sum)
+ *   mlp     B200_MLP_NONE, B200_MLP_DENSE_RELU2: W_down relu(W_up h)^2
+ * Precision: compute_dtype B200_BF16 = bf16 weights / activations / cache with fp32 accumulation, while norms, attention
+ * scores and weights, gates, the residual stream and the depth average stay fp32; B200_F32 = everything in IEEE fp32 (FMA).
+ * Requests live in cache SLOTS of `capacity` tokens; a step runs a ragged batch (any number of new tokens per slot) on top
+ * of what earlier steps left in the slots.  Logits at a position do not depend on how its request was cut into steps. */
+typedef struct b200_dlm b200_dlm;
+
+enum { B200_MIXER_LATENT_ATTENTION = 1 };
+enum { B200_MLP_NONE = 0, B200_MLP_DENSE_RELU2 = 1 };
+
+typedef struct {
+  int mixer;                  /* B200_MIXER_*                                                   */
+  int heads, dim, vdim;       /* per head: query/key size, value size                           */
+  int kv_rank;                /* size of the cached latent                                      */
+  float scale;                /* multiplies q.k                                                 */
+  int mlp;                    /* B200_MLP_*                                                     */
+  int ff;                     /* hidden size of the feed-forward                                */
+} b200_dlm_layer;
+
+typedef struct {
+  int vocab, width, n_layers;
+  float embedding_scale, residual_mult, norm_eps;
+  int compute_dtype;          /* B200_BF16 or B200_F32                                          */
+  const b200_dlm_layer* layers;
+} b200_dlm_config;
+
+int b200_dlm_create(const b200_dlm_config* cfg, b200_dlm** out);
+/* Tensors under the checkpoint's names ("embed", "l<i>.norm1", "l<i>.mix.q", ..., "final.norm", "head"), bf16 or f32. */
+int b200_dlm_load_tensor(b200_dlm* h, const char* name, const void* data_dev, int dtype, int ndim, const int64_t* shape);
+int b200_dlm_finalize(b200_dlm* h);
+int b200_dlm_destroy(b200_dlm* h);
+/* Allocates the latent cache ([slots][capacity][kv_rank] per layer) and the step buffers (up to max_step_tokens new tokens
+ * and max_want logit rows per step).  use_tc = 1: bf16 linears of eligible shapes run on the LM's tcgen05 GEMM. */
+int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_tokens, int max_want, void* stream);
+int b200_dlm_cache_end(b200_dlm* h);
+int b200_dlm_set_stream(b200_dlm* h, void* stream);
+int b200_dlm_set_option(b200_dlm* h, const char* name, int value);   /* "use_tc", "trace_layers", "attn_split" */
+/* Gives a slot back: its length becomes 0 (the next request that gets the slot starts at position 0). */
+int b200_dlm_release(b200_dlm* h, int slot);
+int b200_dlm_slot_length(b200_dlm* h, int slot);
+/* One step: entry e appends counts[e] tokens (tokens_host, concatenated) to slot slots[e]; want_host lists n_want indices into
+ * the concatenated tokens whose logits are wanted -> logits_dev f32 [n_want][vocab] (also kept for b200_dlm_sample).
+ * Host arrays are int32.  Enqueues on the stream; does not synchronise. */
+int b200_dlm_step(b200_dlm* h, int n_entries, const int32_t* slots_host, const int32_t* counts_host,
+                  const int32_t* tokens_host, int n_want, const int32_t* want_host, float* logits_dev);
+/* Samples one token per logit row of the last step with the LM's sampler (b200_op_sample): noise f32 [n_want][min(top_k, vocab)]
+ * Exp(1) draws or NULL when use_sampling = 0 (greedy, first maximum). */
+int b200_dlm_sample(b200_dlm* h, const float* noise_dev, int use_sampling, float temp, int top_k, int64_t* out_dev);
+/* Debug / test hand-offs of the last step, copied device-to-device: "layers" f32 [n_layers][tokens][width] (needs option
+ * trace_layers = 1: what each layer hands on), "logits" f32 [n_want][vocab]. */
+int b200_dlm_read_buffer(b200_dlm* h, const char* name, void* dst_dev, int64_t capacity_bytes, int64_t* nbytes);
+/* HBM bytes one step must move / FLOPs it must do for `tokens` new tokens on top of `context` cached ones (roofline of bench.py) */
+int64_t b200_dlm_algorithmic_bytes(b200_dlm* h, int tokens, int context);
+int64_t b200_dlm_algorithmic_flops(b200_dlm* h, int tokens, int context);
 
 /* ------------------------------------------------------------------------------------------ */
 /* Kernel-level entry points (used by the parity tests; same kernels the handles launch)        */

@@ -14,7 +14,7 @@ LIB_PATH = Path(__file__).resolve().parent / "_C" / "libmoshi_b200.so"
 
 B200_OK, B200_ERR_INVALID, B200_ERR_SHAPE, B200_ERR_STATE, B200_ERR_CUDA, B200_ERR_MISSING = range(6)
 B200_F32, B200_BF16, B200_F16, B200_I64, B200_U8, B200_I8 = range(6)
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 
 class MimiConfigC(C.Structure):
@@ -39,6 +39,16 @@ class LMConfigC(C.Structure):
         ("depformer_num_layers", C.c_int), ("depformer_ffn_hidden", C.c_int), ("delays", C.c_int * 33),
         ("quantize", C.c_int), ("extra_heads_num_heads", C.c_int), ("extra_heads_dim", C.c_int),
     ]
+
+
+class DLMLayerC(C.Structure):
+    _fields_ = [("mixer", C.c_int), ("heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int), ("kv_rank", C.c_int),
+                ("scale", C.c_float), ("mlp", C.c_int), ("ff", C.c_int)]
+
+
+class DLMConfigC(C.Structure):
+    _fields_ = [("vocab", C.c_int), ("width", C.c_int), ("n_layers", C.c_int), ("embedding_scale", C.c_float),
+                ("residual_mult", C.c_float), ("norm_eps", C.c_float), ("compute_dtype", C.c_int), ("layers", C.POINTER(DLMLayerC))]
 
 
 _P = C.c_void_p
@@ -109,6 +119,22 @@ _PROTOTYPES: dict[str, tuple[tp.Any, list]] = {
     "b200_lm_get_offset_cpu": (C.c_int64, [_P]),
     "b200_lm_set_offset_cpu": (_I, [_P, C.c_int64]),
     "b200_lm_error_flags": (_I, [_P, C.POINTER(_I)]),
+    # decoder LM (text-only layer-list models)
+    "b200_dlm_create": (_I, [C.POINTER(DLMConfigC), C.POINTER(_P)]),
+    "b200_dlm_load_tensor": (_I, [_P, C.c_char_p, _P, _I, _I, C.POINTER(C.c_int64)]),
+    "b200_dlm_finalize": (_I, [_P]),
+    "b200_dlm_destroy": (_I, [_P]),
+    "b200_dlm_cache_begin": (_I, [_P, _I, _I, _I, _I, _P]),
+    "b200_dlm_cache_end": (_I, [_P]),
+    "b200_dlm_set_stream": (_I, [_P, _P]),
+    "b200_dlm_set_option": (_I, [_P, C.c_char_p, _I]),
+    "b200_dlm_release": (_I, [_P, _I]),
+    "b200_dlm_slot_length": (_I, [_P, _I]),
+    "b200_dlm_step": (_I, [_P, _I, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32), _I, C.POINTER(C.c_int32), _P]),
+    "b200_dlm_sample": (_I, [_P, _P, _I, C.c_float, _I, _P]),
+    "b200_dlm_read_buffer": (_I, [_P, C.c_char_p, _P, C.c_int64, C.POINTER(C.c_int64)]),
+    "b200_dlm_algorithmic_bytes": (C.c_int64, [_P, _I, _I]),
+    "b200_dlm_algorithmic_flops": (C.c_int64, [_P, _I, _I]),
     # one frame for every session slot, host buffers
     "b200_frame_create": (_I, [_P, _P, _I, _I, _I, _I, _P, C.POINTER(_P)]),
     "b200_frame_destroy": (_I, [_P]),
@@ -144,20 +170,30 @@ class B200Error(RuntimeError):
         self.code = code
 
 
+# A partial build that holds only the text-only decoder LM (and the GEMMs it shares with the Moshi LM): what a fresh checkout
+# compiles when only such a model is served.  The full library, when present, is always preferred.
+DECODER_LIB_PATH = LIB_PATH.with_name("libmoshi_b200_decoder.so")
+
+
 def lib() -> C.CDLL:
     global _lib
     if _lib is None:
-        if not LIB_PATH.exists():
+        path = LIB_PATH if LIB_PATH.exists() else DECODER_LIB_PATH
+        if not path.exists():
             raise RuntimeError(
                 f"{LIB_PATH} is missing: the B200 path has no CPU fallback. Build it with "
                 "`python -m moshi_b200.build` (needs nvcc; cross-compiles for sm_100a).")
-        handle = C.CDLL(str(LIB_PATH))
+        handle = C.CDLL(str(path))
         for name, (res, args) in _PROTOTYPES.items():
-            fn = getattr(handle, name)
+            fn = getattr(handle, name, None)
+            if fn is None:
+                if path == LIB_PATH:
+                    raise RuntimeError(f"{path} does not export {name}; rebuild")
+                continue                      # the partial build has the decoder LM's entry points only
             fn.restype = res
             fn.argtypes = args
         if handle.b200_abi_version() != ABI_VERSION:
-            raise RuntimeError("libmoshi_b200.so ABI version mismatch; rebuild")
+            raise RuntimeError(f"{path.name} ABI version mismatch; rebuild")
         _lib = handle
     return _lib
 

@@ -264,3 +264,94 @@ def tiny_lm_config(**over) -> LMConfig:
                 depformer_num_heads=2, depformer_num_layers=2)
     base.update(over)
     return LMConfig(**base)
+
+
+# ---------------------------------------------------------------------------------------------------
+# Decoder LMs given as a list of layers (text-only; no reference counterpart)
+# ---------------------------------------------------------------------------------------------------
+MIXERS = {"latent_attention": 1}            # name in config.json -> B200_MIXER_*
+MLP_KINDS = {None: 0, "dense": 1}           # "mlp.kind" (or a null "mlp") -> B200_MLP_*
+
+
+@dataclass
+class DecoderLayerConfig:
+    """One entry of ``layers``: the token mixer with its sizes, and the feed-forward (``mlp_kind`` None = the layer has none)."""
+    type: str
+    heads: int
+    dim: int
+    vdim: int
+    kv_rank: int
+    scale: float
+    mlp_kind: tp.Optional[str] = "dense"
+    ff: int = 0
+
+    @staticmethod
+    def from_dict(d: dict) -> "DecoderLayerConfig":
+        kind = d["type"]
+        if kind not in MIXERS:
+            raise ValueError(f"unknown mixer type {kind!r} (known: {sorted(MIXERS)})")
+        m = d["mixer"]
+        mlp = d.get("mlp")
+        if mlp is not None and mlp.get("kind") not in MLP_KINDS:
+            raise ValueError(f"unknown feed-forward kind {mlp.get('kind')!r}")
+        return DecoderLayerConfig(type=kind, heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]), kv_rank=int(m["kv_rank"]),
+                                  scale=float(m["scale"]), mlp_kind=None if mlp is None else mlp["kind"],
+                                  ff=0 if mlp is None else int(mlp["ff"]))
+
+    def to_dict(self) -> dict:
+        return {"type": self.type,
+                "mixer": {"heads": self.heads, "dim": self.dim, "vdim": self.vdim, "kv_rank": self.kv_rank, "scale": self.scale},
+                "mlp": None if self.mlp_kind is None else {"kind": self.mlp_kind, "ff": self.ff}}
+
+
+@dataclass
+class DecoderLMConfig:
+    """``config.json`` of a layer-list decoder LM.  ``architecture`` selects the block arrangement; "Likosun" is a parallel block
+    (one layer norm feeds mixer and feed-forward), sigmoid-gated sublayer results, a residual multiplier, and a depth-weighted
+    average of all earlier layer results in front of every layer."""
+    architecture: str
+    vocab: int
+    width: int
+    layers: tp.List[DecoderLayerConfig]
+    embedding_scale: float = 1.0
+    residual_mult: float = 1.0
+    norm_eps: float = 1e-6
+
+    @staticmethod
+    def from_dict(d: dict) -> "DecoderLMConfig":
+        arch = d.get("architecture")
+        if arch not in DECODER_ARCHITECTURES:
+            raise ValueError(f"unknown architecture {arch!r} (known: {sorted(DECODER_ARCHITECTURES)})")
+        return DecoderLMConfig(architecture=arch, vocab=int(d["vocab"]), width=int(d["width"]),
+                               layers=[DecoderLayerConfig.from_dict(x) for x in d["layers"]],
+                               embedding_scale=float(d["embedding"]["scale"]), residual_mult=float(d["residual_mult"]),
+                               norm_eps=float(d["norm"]["eps"]))
+
+    @staticmethod
+    def from_json(path: str) -> "DecoderLMConfig":
+        with open(path) as f:
+            return DecoderLMConfig.from_dict(json.load(f))
+
+    def to_dict(self) -> dict:
+        return {"architecture": self.architecture, "embedding": {"scale": self.embedding_scale},
+                "layers": [x.to_dict() for x in self.layers], "norm": {"eps": self.norm_eps},
+                "residual_mult": self.residual_mult, "vocab": self.vocab, "width": self.width}
+
+    def tensor_shapes(self) -> dict:
+        """Checkpoint names -> shapes (linear weights are [out, in])."""
+        W = self.width
+        out = {"embed": (self.vocab, W)}
+        for i, L in enumerate(self.layers):
+            p = f"l{i}."
+            out.update({p + "norm1": (W,), p + "norm1.b": (W,), p + "mix.q": (L.heads * L.dim, W), p + "mix.dkv": (L.kv_rank, W),
+                        p + "mix.dkv.norm": (L.kv_rank,), p + "mix.uk": (L.heads * L.dim, L.kv_rank),
+                        p + "mix.uv": (L.heads * L.vdim, L.kv_rank), p + "mix.sink": (L.heads,), p + "mix.o": (W, L.heads * L.vdim),
+                        p + "rg1": (W, W), p + "rg1.b": (W,), p + "dwa": (i + 2,)})
+            if L.mlp_kind is not None:
+                out.update({p + "mlp.up": (L.ff, W), p + "mlp.down": (W, L.ff), p + "rg2": (W, W), p + "rg2.b": (W,)})
+        out.update({"final.norm": (W,), "final.norm.b": (W,), "head": (self.vocab, W)})
+        return out
+
+
+# architecture name in config.json -> configuration class (the model registry of the text-only decoder LMs)
+DECODER_ARCHITECTURES: dict = {"Likosun": DecoderLMConfig}

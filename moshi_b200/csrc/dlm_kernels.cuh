@@ -1,0 +1,403 @@
+// Kernels of the decoder-LM handle (dlm.cu): the mechanisms a layer-list language model is assembled from.
+//   T = activation / weight / cache type (bf16, or float for the all-fp32 mode); every reduction, norm, score, softmax,
+//   gate, the residual stream and the depth average are fp32 in both modes.
+#pragma once
+
+#include "common.cuh"
+
+namespace b200 {
+namespace dlm {
+
+using bf16 = __nv_bfloat16;
+
+enum { ERR_TOKEN = 1 };      // device error flag: a token id outside the embedding table
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// sum over the block (blockDim.x a multiple of 32, <= 1024); every thread gets the result
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = l < nw ? red[l] : 0.f;
+  return warp_sum(t);
+}
+
+__device__ __forceinline__ float sigmoidf(float z) { return 1.f / (1.f + expf(-z)); }
+
+// layer norm with weight and bias of one fp32 row (two passes: mean, then the mean of squared deviations) -> T
+template <typename T>
+__device__ __forceinline__ void block_layernorm(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                                                T* __restrict__ out, int W, float eps, float* red) {
+  float s = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) s += x[i];
+  const float mean = block_sum(s, red) / (float)W;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) { const float d = x[i] - mean; q += d * d; }
+  const float rstd = 1.f / sqrtf(block_sum(q, red) / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) out[i] = from_f<T>((x[i] - mean) * rstd * w[i] + b[i]);
+}
+
+// x = table[token] * scale -> the layer-input stream and slot 0 of the per-layer result stack
+template <typename T>
+__global__ void __launch_bounds__(256) embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table, int vocab, int W, float scale,
+                                                    float* __restrict__ xin, float* __restrict__ x0, int* __restrict__ err) {
+  const int t = blockIdx.x;
+  int id = tokens[t];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(err, ERR_TOKEN);
+    id = 0;
+  }
+  const T* row = table + (long long)id * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = to_f(row[i]) * scale;
+    xin[(long long)t * W + i] = v;
+    x0[(long long)t * W + i] = v;
+  }
+}
+
+// h[row] = layernorm(x[rows ? rows[row] : row])
+template <typename T>
+__global__ void __launch_bounds__(256) layernorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+                                                        const float* __restrict__ b, T* __restrict__ out, int W, float eps) {
+  __shared__ float red[32];
+  const int src = rows ? rows[blockIdx.x] : blockIdx.x;
+  block_layernorm<T>(x + (long long)src * W, w, b, out + (long long)blockIdx.x * W, W, eps, red);
+}
+
+// End of a parallel block with gated residuals and a depth-weighted average, one CTA per token:
+//   X_new = x + mult * (mix * sigmoid(g1 + b1) + ff * sigmoid(g2 + b2));  stack[li + 1] = X_new
+//   x    <- sum_{j <= li + 1} avg[j] * stack[j]            (what the next layer, or the output norm, reads)
+//   h    <- layernorm(x) with the NEXT layer's norm (when given)
+template <typename T>
+__global__ void __launch_bounds__(256) block_end_kernel(float* __restrict__ xin, const T* __restrict__ mix, const T* __restrict__ ff,
+                                                        const T* __restrict__ proj, long long ldp, int off_g1, int off_g2,
+                                                        const float* __restrict__ b1, const float* __restrict__ b2, float mult,
+                                                        float* __restrict__ stack, long long stack_stride, int li,
+                                                        const float* __restrict__ avg, float* __restrict__ trace,
+                                                        const float* __restrict__ nw, const float* __restrict__ nb, T* __restrict__ h,
+                                                        int W, float eps) {
+  __shared__ float red[32];
+  const long long t = blockIdx.x;
+  float* x = xin + t * W;
+  const T* pr = proj + t * ldp;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float v = to_f(mix[t * W + i]) * sigmoidf(to_f(pr[off_g1 + i]) + b1[i]);
+    if (ff) v += to_f(ff[t * W + i]) * sigmoidf(to_f(pr[off_g2 + i]) + b2[i]);
+    const float xn = x[i] + mult * v;
+    stack[(long long)(li + 1) * stack_stride + t * W + i] = xn;
+    float acc = 0.f;
+    for (int j = 0; j <= li; ++j) acc += avg[j] * stack[(long long)j * stack_stride + t * W + i];
+    acc += avg[li + 1] * xn;
+    x[i] = acc;
+    if (trace) trace[t * W + i] = acc;
+  }
+  if (nw) {
+    __syncthreads();
+    block_layernorm<T>(x, nw, nb, h + t * W, W, eps, red);
+  }
+}
+
+// latent of the new tokens: c = raw / sqrt(mean(raw^2) + eps) * w, appended to the slot's cache rows; one warp per token
+template <typename T>
+__global__ void __launch_bounds__(128) latent_append_kernel(const T* __restrict__ proj, long long ldp, int off, const float* __restrict__ w,
+                                                            T* __restrict__ cache, int cap, int r, const int* __restrict__ tok_slot,
+                                                            const int* __restrict__ tok_pos, int n_tok, float eps) {
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5), l = threadIdx.x & 31;
+  if (t >= n_tok) return;
+  const T* raw = proj + (long long)t * ldp + off;
+  float s = 0.f;
+  for (int i = l; i < r; i += 32) { const float v = to_f(raw[i]); s += v * v; }
+  const float rs = 1.f / sqrtf(warp_sum(s) / (float)r + eps);
+  T* dst = cache + ((long long)tok_slot[t] * cap + tok_pos[t]) * r;
+  for (int i = l; i < r; i += 32) dst[i] = from_f<T>(to_f(raw[i]) * rs * w[i]);
+}
+
+// out = relu(x)^2
+template <typename T>
+__global__ void __launch_bounds__(256) relu2_kernel(const T* __restrict__ proj, long long ldp, int off, T* __restrict__ out, int F, long long n) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n) return;
+  const long long t = i / F; const int f = (int)(i - t * F);
+  const float v = fmaxf(to_f(proj[t * ldp + off + f]), 0.f);
+  out[i] = from_f<T>(v * v);
+}
+
+// C[z][M][N] = alpha * A[z][M][K] . B[z][N][K]^T on the CUDA cores (fp32 FMA; inputs converted on load): the all-fp32 mode's
+// linear, the per-head products around the latent attention, and the bf16 mode's linear for shapes the tcgen05 GEMM does not take.
+// A row's sum runs over k in order whatever M is: a token's result does not depend on what else is in the step.
+template <typename TA, typename TB, typename TC>
+__global__ void __launch_bounds__(256) gemm_nt_kernel(const TA* __restrict__ A, long long lda, long long sa, const TB* __restrict__ B,
+                                                      long long ldb, long long sb, TC* __restrict__ C, long long ldc, long long sc,
+                                                      int M, int N, int K, float alpha) {
+  constexpr int BM = 64, BN = 64, BK = 16;
+  __shared__ float As[BK][BM + 1], Bs[BK][BN + 1];
+  A += (long long)blockIdx.z * sa; B += (long long)blockIdx.z * sb; C += (long long)blockIdx.z * sc;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int rr = ty + 16 * i, kk = k0 + tx;
+      As[tx][rr] = (m0 + rr < M && kk < K) ? to_f(A[(long long)(m0 + rr) * lda + kk]) : 0.f;
+      Bs[tx][rr] = (n0 + rr < N && kk < K) ? to_f(B[(long long)(n0 + rr) * ldb + kk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { a[i] = As[k][ty + 16 * i]; b[i] = Bs[k][tx + 16 * i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int m = m0 + ty + 16 * i, n = n0 + tx + 16 * j;
+      if (m < M && n < N) C[(long long)m * ldc + n] = from_f<TC>(alpha * acc[i][j]);
+    }
+}
+
+// [H*d][r] -> [H][r][d] (per-head transpose, done once at load: the query-side fold of W_uk wants it k-major)
+template <typename T>
+__global__ void head_transpose_kernel(const T* __restrict__ in, T* __restrict__ out, int H, int d, int r) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= (long long)H * d * r) return;
+  const int c = (int)(i % r); const long long hd = i / r; const int dd = (int)(hd % d); const int hh = (int)(hd / d);
+  out[((long long)hh * r + c) * d + dd] = in[i];
+}
+
+template <typename TI, typename TO>
+__global__ void convert_kernel(const TI* __restrict__ in, TO* __restrict__ out, long long n) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i < n) out[i] = from_f<TO>(to_f(in[i]));
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Latent attention.  Rows are (token, head) pairs, head fastest; a tile is up to 4 * RPW consecutive rows of ONE cache slot.
+// qa[row][r] is the query folded through W_uk and the score scale, so that score(row, j) = qa[row] . c[j] against the cached
+// latents themselves and the value side is out[row] = sum_j p_j c[j] (W_uv is applied afterwards).  Causal: key j <= the
+// row's position.  The softmax denominator holds one extra term exp(sink[head]) that has no value.
+//   lane l owns latent elements l, l + 32, ...; a 32-key tile is staged in shared memory and shared by the CTA's 4 warps;
+//   per row and key tile: 32 partial dots are transposed-reduced (8 keys at a time) so that lane L ends with the score of
+//   key (L & 3) * 8 + (L >> 2); then one online-softmax update and the weighted sum.
+//   nsplit > 1: CTA (tile, s) covers a contiguous share of the key tiles and leaves (m, l, unnormalised sum) for the merge.
+// ---------------------------------------------------------------------------------------------------------------------------
+struct AttnParams {
+  const float* qa;          // [rows][r]
+  const void* cache;        // T [slots][cap][r]
+  const float* sink;        // [H]
+  const int* tile_row0;     // first row of the tile
+  const int* tile_rows;     // rows in the tile
+  const int* tile_slot;
+  const int* tok_pos;       // position of every token of the step in its slot
+  float* out;               // [rows][r]
+  float* part;              // nsplit > 1: [tile][split][rows_per_tile][r + 2]
+  int cap, r, H, nsplit;
+};
+
+template <typename T, int NCH, int RPW>
+__global__ void __launch_bounds__(128) latent_attn_kernel(AttnParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* cs = reinterpret_cast<T*>(smem_raw);            // [32][r]
+  constexpr int KT = 32;
+  const int tile = blockIdx.x, split = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = p.r, H = p.H;
+  const int row0 = p.tile_row0[tile], nrows = p.tile_rows[tile];
+  const T* cbase = static_cast<const T*>(p.cache) + (long long)p.tile_slot[tile] * p.cap * r;
+  const int kmax = p.tok_pos[(row0 + nrows - 1) / H];          // rows are ordered by token: the last row sees the most keys
+  const int n_kt = kmax / KT + 1;
+  const int per = (n_kt + p.nsplit - 1) / p.nsplit;
+  const int kt0 = split * per, kt1 = min(n_kt, kt0 + per);
+
+  float q[RPW][NCH], o[RPW][NCH], m[RPW], lsum[RPW];
+  int pos[RPW];
+#pragma unroll
+  for (int i = 0; i < RPW; ++i) {
+    const int lr = warp * RPW + i;
+    const bool valid = lr < nrows;
+    const int g = row0 + (valid ? lr : 0);
+    pos[i] = valid ? p.tok_pos[g / H] : -1;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int e = lane + 32 * c;
+      q[i][c] = (valid && e < r) ? p.qa[(long long)g * r + e] : 0.f;
+      o[i][c] = 0.f;
+    }
+    // the sink enters once: the first split starts from (m = sink, l = 1); the others from nothing
+    if (split == 0 && valid) { m[i] = p.sink[g % H]; lsum[i] = lane == 0 ? 1.f : 0.f; }
+    else { m[i] = -INFINITY; lsum[i] = 0.f; }
+  }
+
+  for (int kt = kt0; kt < kt1; ++kt) {
+    const int j0 = kt * KT;
+    const int nk = min(KT, kmax + 1 - j0);
+    __syncthreads();
+    {   // stage keys j0 .. j0 + nk - 1: one contiguous span of the slot's cache
+      const T* src = cbase + (long long)j0 * r;
+      const int n = nk * r;
+      if (((r * (int)sizeof(T)) & 15) == 0) {
+        const int n16 = n * (int)sizeof(T) / 16;
+        const uint4* s4 = reinterpret_cast<const uint4*>(src);
+        uint4* d4 = reinterpret_cast<uint4*>(cs);
+        for (int i = threadIdx.x; i < n16; i += 128) d4[i] = s4[i];
+      } else {
+        for (int i = threadIdx.x; i < n; i += 128) cs[i] = src[i];
+      }
+    }
+    __syncthreads();
+    float sc[RPW];
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) sc[i] = 0.f;
+#pragma unroll
+    for (int g8 = 0; g8 < 4; ++g8) {
+      if (g8 * 8 >= nk) break;                                   // uniform over the CTA
+      float part[RPW][8];
+#pragma unroll
+      for (int i = 0; i < RPW; ++i)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) part[i][k] = 0.f;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const int e = lane + 32 * c;
+        if (e < r) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int kk = g8 * 8 + k;
+            const float cv = kk < nk ? to_f(cs[kk * r + e]) : 0.f;
+#pragma unroll
+            for (int i = 0; i < RPW; ++i) part[i][k] = fmaf(q[i][c], cv, part[i][k]);
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < RPW; ++i) {
+        float v4[4], v2[2];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float send = (lane & 16) ? part[i][k] : part[i][k + 4];
+          const float keep = (lane & 16) ? part[i][k + 4] : part[i][k];
+          v4[k] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const float send = (lane & 8) ? v4[k] : v4[k + 2];
+          const float keep = (lane & 8) ? v4[k + 2] : v4[k];
+          v2[k] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+        }
+        const float send = (lane & 4) ? v2[0] : v2[1];
+        const float keep = (lane & 4) ? v2[1] : v2[0];
+        float v1 = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+        v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+        v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+        // every lane now holds the score of key g8 * 8 + (lane >> 2); lanes with (lane & 3) == g8 keep it
+        if ((lane & 3) == g8) sc[i] = v1;
+      }
+    }
+    const int mykey = j0 + (lane & 3) * 8 + (lane >> 2);
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) {
+      const bool seen = mykey <= pos[i] && mykey <= kmax;
+      const float s = seen ? sc[i] : -INFINITY;
+      const float mn = fmaxf(m[i], warp_max(s));
+      float pj = 0.f;
+      if (mn > -INFINITY) {                                       // uniform over the warp
+        const float corr = expf(m[i] - mn);                       // m = -inf -> 0
+        pj = seen ? expf(s - mn) : 0.f;
+        lsum[i] = lsum[i] * corr + pj;
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) o[i][c] *= corr;
+        m[i] = mn;
+      }
+      sc[i] = pj;
+    }
+    for (int k = 0; k < nk; ++k) {
+      const int srcl = ((k & 7) << 2) | (k >> 3);
+      float pk[RPW];
+      bool any = false;
+#pragma unroll
+      for (int i = 0; i < RPW; ++i) { pk[i] = __shfl_sync(0xffffffffu, sc[i], srcl); any |= pk[i] != 0.f; }
+      if (!any) continue;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const int e = lane + 32 * c;
+        if (e < r) {
+          const float cv = to_f(cs[k * r + e]);
+#pragma unroll
+          for (int i = 0; i < RPW; ++i) o[i][c] = fmaf(pk[i], cv, o[i][c]);
+        }
+      }
+    }
+  }
+
+#pragma unroll
+  for (int i = 0; i < RPW; ++i) {
+    const int lr = warp * RPW + i;
+    if (lr >= nrows) continue;
+    const float l = warp_sum(lsum[i]);
+    if (p.nsplit == 1) {
+      const float inv = 1.f / l;
+      float* dst = p.out + (long long)(row0 + lr) * r;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) { const int e = lane + 32 * c; if (e < r) dst[e] = o[i][c] * inv; }
+    } else {
+      float* dst = p.part + (((long long)tile * p.nsplit + split) * (4 * RPW) + lr) * (r + 2);
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) { const int e = lane + 32 * c; if (e < r) dst[e] = o[i][c]; }
+      if (lane == 0) { dst[r] = m[i]; dst[r + 1] = l; }
+    }
+  }
+}
+
+// merges the splits of one row: out = sum_s o_s exp(m_s - M) / sum_s l_s exp(m_s - M); one warp per row
+__global__ void __launch_bounds__(128) latent_attn_merge_kernel(const float* __restrict__ part, const int* __restrict__ tile_row0,
+                                                                const int* __restrict__ tile_rows, float* __restrict__ out, int r,
+                                                                int nsplit, int rows_per_tile) {
+  const int tile = blockIdx.x, lane = threadIdx.x & 31;
+  for (int lr = threadIdx.x >> 5; lr < tile_rows[tile]; lr += 4) {
+    const float* base = part + ((long long)tile * nsplit * rows_per_tile + lr) * (r + 2);
+    const long long ss = (long long)rows_per_tile * (r + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, base[s * ss + r]);
+    float L = 0.f;
+    for (int s = 0; s < nsplit; ++s) { const float ms = base[s * ss + r]; if (ms > -INFINITY) L += base[s * ss + r + 1] * expf(ms - M); }
+    const float inv = 1.f / L;
+    float* dst = out + (long long)(tile_row0[tile] + lr) * r;
+    for (int e = lane; e < r; e += 32) {
+      float acc = 0.f;
+      for (int s = 0; s < nsplit; ++s) { const float ms = base[s * ss + r]; if (ms > -INFINITY) acc += base[s * ss + e] * expf(ms - M); }
+      dst[e] = acc * inv;
+    }
+  }
+}
+
+// bf16 rows with a padded stride -> fp32 [rows][V]
+__global__ void rows_to_f32_kernel(const bf16* __restrict__ in, long long ld, float* __restrict__ out, int V, long long n) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n) return;
+  const long long row = i / V;
+  out[i] = __bfloat162float(in[row * ld + (i - row * V)]);
+}
+
+// logits f32 -> bf16 rows for the LM's sampler
+__global__ void logits_to_bf16_kernel(const float* __restrict__ in, bf16* __restrict__ out, long long n) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i < n) out[i] = __float2bfloat16_rn(in[i]);
+}
+
+}  // namespace dlm
+}  // namespace b200

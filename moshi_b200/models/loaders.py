@@ -15,9 +15,10 @@ from pathlib import Path
 
 import torch
 
-from ..config import LMConfig, MimiConfig
+from ..config import DECODER_ARCHITECTURES, DecoderLMConfig, LMConfig, MimiConfig
 from ..synth import iter_synth_lm_tensors, synth_mimi_state_dict
 from .compression import MimiModel
+from .decoder_lm import DecoderLM
 from .lm import LMModel
 
 SAMPLE_RATE = 24000
@@ -84,6 +85,68 @@ def get_moshi_lm(filename: str | Path | None, lm_kwargs: dict | None = None,
     else:
         tensors = torch.load(filename, "cpu")["fsdp_best_state"]["model"]
     return LMModel(cfg, tensors, device=device, dtype=dtype)
+
+
+def read_safetensors(path: str | Path) -> tp.Iterator[tuple[str, torch.Tensor]]:
+    """Streams (name, tensor) out of a safetensors file: 8-byte little-endian header length, a JSON header (name -> dtype, shape,
+    data_offsets), then the data.  bf16 / f16 / f32 / i32 / i64 / u8 / i8 tensors."""
+    import numpy as np
+    kinds = {"BF16": (torch.bfloat16, 2), "F16": (torch.float16, 2), "F32": (torch.float32, 4), "I32": (torch.int32, 4),
+             "I64": (torch.int64, 8), "U8": (torch.uint8, 1), "I8": (torch.int8, 1)}
+    with open(path, "rb") as f:
+        n = int.from_bytes(f.read(8), "little")
+        header = json.loads(f.read(n))
+        base = 8 + n
+        for name, meta in header.items():
+            if name == "__metadata__":
+                continue
+            if meta["dtype"] not in kinds:
+                raise ValueError(f"{path}: tensor {name!r} has dtype {meta['dtype']}")
+            dt, _ = kinds[meta["dtype"]]
+            lo, hi = meta["data_offsets"]
+            f.seek(base + lo)
+            raw = np.frombuffer(f.read(hi - lo), dtype=np.uint8).copy()
+            yield name, torch.from_numpy(raw).view(dt).reshape(meta["shape"])
+
+
+def model_class(config: dict):
+    """The model registry: which class serves a ``config.json``.  Text-only decoder LMs name their ``architecture``; the Moshi LM's
+    JSON (``configs/moshi_7b_202409.json``) has none and is recognised by its own keys."""
+    arch = config.get("architecture")
+    if arch in DECODER_ARCHITECTURES:
+        return DecoderLM
+    if arch is None and "dep_q" in config and "n_q" in config:
+        return LMModel
+    raise ValueError(f"no model class for architecture {arch!r} (decoder LMs: {sorted(DECODER_ARCHITECTURES)})")
+
+
+def get_decoder_lm(model_dir: str | Path | None, config: dict | DecoderLMConfig | None = None, device: torch.device | str = "cuda",
+                   dtype: torch.dtype = torch.bfloat16, synth_seed: int = 99, use_tc: bool = True) -> DecoderLM:
+    """A text-only decoder LM from a folder holding ``config.json`` + ``model.safetensors``; with ``model_dir=None`` the given
+    configuration gets seeded synthetic weights (``moshi_b200.synth.iter_synth_decoder_tensors``), as ``get_moshi_lm`` does."""
+    if model_dir is not None:
+        raw = json.loads((Path(model_dir) / "config.json").read_text())
+        if model_class(raw) is not DecoderLM:
+            raise ValueError(f"{model_dir}: not a decoder LM configuration")
+        cfg = DECODER_ARCHITECTURES[raw["architecture"]].from_dict(raw)
+        tensors: tp.Any = read_safetensors(Path(model_dir) / "model.safetensors")
+    else:
+        if config is None:
+            raise ValueError("get_decoder_lm: give a model folder or a configuration")
+        cfg = config if isinstance(config, DecoderLMConfig) else DecoderLMConfig.from_dict(config)
+        from ..synth import iter_synth_decoder_tensors
+        tensors = iter_synth_decoder_tensors(cfg, seed=synth_seed, device=device)
+    return DecoderLM(cfg, tensors, device=device, dtype=dtype, use_tc=use_tc)
+
+
+def get_model(model_dir: str | Path, device: torch.device | str = "cuda", dtype: torch.dtype = torch.bfloat16, **kwargs):
+    """Model folder -> the registered class for its ``config.json``."""
+    raw = json.loads((Path(model_dir) / "config.json").read_text())
+    cls = model_class(raw)
+    if cls is DecoderLM:
+        return get_decoder_lm(model_dir, device=device, dtype=dtype, **kwargs)
+    weights = Path(model_dir) / MOSHI_NAME
+    return get_moshi_lm(weights if weights.exists() else None, lm_kwargs=raw, device=device, dtype=dtype, **kwargs)
 
 
 @dataclass

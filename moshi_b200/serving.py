@@ -239,3 +239,123 @@ class SessionPool:
                 pcm[slot] = 0.0
                 updates[slot] = NODATA
         return ready
+
+
+# ---------------------------------------------------------------------------------------------------
+# Text requests over a decoder LM's cache slots
+# ---------------------------------------------------------------------------------------------------
+class TokenScheduler:
+    """Continuous batching for ``DecoderLMGen``: requests are admitted into free cache slots, every step takes the next prompt
+    portion (at most ``max_step_tokens`` tokens over all requests) or the one token a decoding request produced last, and a
+    finished request gives its slot back at once.  Two ways in:
+
+    * ``feed(request_id, tokens, want)`` + ``run_step()``: the caller supplies every token (replaying a trace, scoring);
+    * ``submit(request_id, prompt, max_new_tokens)`` + ``run()``: prompt portions, then sampled tokens until the budget or ``eos``.
+    """
+
+    def __init__(self, gen, eos: int | None = None):
+        self.gen = gen
+        self.eos = eos
+        self._free = list(range(gen.slots - 1, -1, -1))
+        self._slot: dict[str, int] = {}
+        self._pending: dict[str, list[int]] = {}          # tokens not yet run, per request
+        self._want: dict[str, list[int]] = {}             # indices into _pending whose logits are wanted
+        self._budget: dict[str, int] = {}                 # tokens still to generate
+        self.generated: dict[str, list[int]] = {}
+        self._queue: list[str] = []                       # submitted, waiting for a slot
+
+    @property
+    def free_slots(self) -> int:
+        return len(self._free)
+
+    def slot_of(self, request_id: str) -> int:
+        return self._slot[request_id]
+
+    def _admit(self, request_id: str) -> int:
+        if request_id not in self._slot:
+            if not self._free:
+                raise RuntimeError("no free cache slot")
+            self._slot[request_id] = self._free.pop()
+            self._pending[request_id] = []
+            self._want[request_id] = []
+        return self._slot[request_id]
+
+    def end(self, request_id: str) -> None:
+        """The request is finished: its slot (and what it holds in the cache) is given back."""
+        slot = self._slot.pop(request_id)
+        self.gen.release(slot)
+        self._free.append(slot)
+        self._pending.pop(request_id, None)
+        self._want.pop(request_id, None)
+        self._budget.pop(request_id, None)
+
+    def feed(self, request_id: str, tokens, want=()) -> None:
+        self._admit(request_id)
+        base = len(self._pending[request_id])
+        self._pending[request_id].extend(int(t) for t in tokens)
+        self._want[request_id].extend(base + int(w) for w in want)
+
+    def submit(self, request_id: str, prompt, max_new_tokens: int) -> None:
+        self.generated[request_id] = []
+        self._budget[request_id] = int(max_new_tokens)
+        self._queue.append(request_id)
+        self._prompts = getattr(self, "_prompts", {})
+        self._prompts[request_id] = [int(t) for t in prompt]
+
+    def run_step(self):
+        """One step over everything pending (cut to the step's token budget, requests in arrival order).  Returns
+        ``{request_id: logits f32 [wanted, vocab]}`` for the requests whose wanted positions ran in this step, or None if
+        nothing was pending."""
+        room = self.gen.max_step_tokens
+        entries, ids, want, per_req = [], [], [], []
+        for rid, toks in self._pending.items():
+            if not toks or room == 0:
+                continue
+            n = min(len(toks), room)
+            base = sum(len(t) for _, t in entries)
+            w = [i for i in self._want[rid] if i < n]
+            spare = self.gen.max_want - len(want)
+            if len(w) > spare:                 # stop in front of the first wanted row that does not fit into this step
+                n, w = w[spare], w[:spare]
+                if n == 0:
+                    continue
+            entries.append((self._slot[rid], toks[:n]))
+            ids.append(rid)
+            per_req.append(len(w))
+            want.extend(base + i for i in w)
+            self._pending[rid] = toks[n:]
+            self._want[rid] = [i - n for i in self._want[rid] if i >= n]
+            room -= n
+        if not entries:
+            return None
+        logits = self.gen.step(entries, want)
+        out, at = {}, 0
+        for rid, k in zip(ids, per_req):
+            if k:
+                out[rid] = logits[at:at + k]
+                at += k
+        return out
+
+    def run(self) -> dict[str, list[int]]:
+        """Runs every submitted request to its end; returns the generated tokens per request."""
+        prompts = getattr(self, "_prompts", {})
+        while self._queue or self._slot:
+            while self._queue and self._free:
+                rid = self._queue.pop(0)
+                p = prompts.pop(rid)
+                self.feed(rid, p, [len(p) - 1])
+            order = [rid for rid, toks in self._pending.items() if toks]
+            got = self.run_step()
+            if got is None:
+                break
+            done_rows = [rid for rid in order if rid in got]
+            if done_rows:
+                toks = self.gen.sample().tolist()
+                for rid, tok in zip(done_rows, toks):
+                    self.generated[rid].append(int(tok))
+                    self._budget[rid] -= 1
+                    if self._budget[rid] <= 0 or (self.eos is not None and tok == self.eos):
+                        self.end(rid)
+                    else:
+                        self.feed(rid, [tok], [0])
+        return self.generated

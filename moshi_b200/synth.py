@@ -17,7 +17,7 @@ import typing as tp
 
 import torch
 
-from .config import LMConfig, MimiConfig
+from .config import DecoderLMConfig, LMConfig, MimiConfig
 
 # Scale of the synthetic codebook entries per RVQ level, as a fraction of the level-0 residual
 # standard deviation (the input-projected latent).  Level l of a residual quantizer sees a
@@ -264,3 +264,28 @@ def tiled_lm_state_dict(cfg: LMConfig, seed: int = 7, block_elems: int = 1 << 25
         start = (start + 9973) % block_elems
         sd[key] = t.view(shape)
     return sd
+
+
+# ----------------------------------------------------------------------------------------------
+# text-only decoder LMs
+# ----------------------------------------------------------------------------------------------
+
+def iter_synth_decoder_tensors(cfg: DecoderLMConfig, seed: int = 99, device="cpu", dtype=torch.bfloat16):
+    """(name, tensor) pairs of a decoder LM under its checkpoint names.  Matrices are uniform with a fan-in bound; norm weights
+    sit around 1, biases and sinks around 0, and the depth-average rows are positive and sum to 1, so that activations keep a
+    sane scale through any number of layers."""
+    gen = _gen(seed, device)
+    for name, shape in cfg.tensor_shapes().items():
+        leaf = name.split(".", 1)[-1] if name.startswith("l") and name[1].isdigit() else name
+        if leaf in ("norm1", "final.norm", "mix.dkv.norm"):
+            t = 1.0 + _uniform(gen, shape, 0.2, device)
+        elif leaf.endswith(".b") or leaf == "mix.sink":
+            t = _uniform(gen, shape, 0.5, device)
+        elif leaf == "dwa":
+            t = torch.rand(shape, generator=gen, device=device) + 0.2
+            t = t / t.sum()
+        elif leaf == "embed":
+            t = _uniform(gen, shape, 1.0, device)
+        else:
+            t = _uniform(gen, shape, math.sqrt(3.0 / shape[-1]), device)
+        yield name, t.to(dtype)
