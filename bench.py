@@ -545,6 +545,146 @@ def b200_arm(args) -> None:
     print(json.dumps(line))
 
 
+# ---------------------------------------------------------------------------------------------
+# --decoder-lm: the text-only decoder LM (Likosun design) beside the Moshi temporal transformer at equal width and depth
+# ---------------------------------------------------------------------------------------------
+DECODER_SIZES = {
+    # name: (width, layers, heads, dim, vdim, kv_rank, ff, vocab)
+    "w2048": (2048, 4, 16, 128, 128, 512, 8192, 32000),
+    "w4096": (4096, 2, 32, 128, 128, 512, 16384, 32000),
+}
+
+
+def _decoder_cfg(size: str):
+    from moshi_b200.config import DecoderLMConfig
+    W, L, H, dk, dv, r, ff, V = DECODER_SIZES[size]
+    lay = {"type": "latent_attention", "mixer": {"heads": H, "dim": dk, "vdim": dv, "kv_rank": r, "scale": dk ** -0.5},
+           "mlp": {"kind": "dense", "ff": ff}}
+    return DecoderLMConfig.from_dict({"architecture": "Likosun", "vocab": V, "width": W, "embedding": {"scale": 1.0},
+                                      "residual_mult": 0.5, "norm": {"eps": 1e-6}, "layers": [lay] * L})
+
+
+def _timed_steps(fn, steps: int, warmup: int) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def decoder_lm_arm(args) -> None:
+    """Prefill (one prompt portion of --prefill-tokens) and decode (--decode-batch requests, one token each, on --context cached
+    tokens) of the decoder LM with random weights, per size; per-class kernel times against their rooflines; and the Moshi
+    temporal transformer (no depformer) at the same width, depth and batch as the closest existing model (it has no prefill)."""
+    import ctypes as C
+    from moshi_b200 import _lib
+    from moshi_b200.config import LMConfig
+    from moshi_b200.models import DecoderLMGen, LMGen, loaders
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    hbm, src = _peaks()
+    pk = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    tf = float(pk.get("bf16_tflops", 1590.0))
+    T, B, ctx = args.prefill_tokens, args.decode_batch, args.context
+    g = torch.Generator().manual_seed(7)
+    out = {"impl": "b200", "mode": "decoder-lm", "dtype": "bf16", "data": "synthetic (random weights)", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
+           "workload": {"prefill_tokens": T, "decode_batch": B, "context": ctx}, "sizes": {}}
+    launches0 = _lib.lib().b200_launch_count()
+    for size in args.decoder_sizes.split(","):
+        cfg = _decoder_cfg(size)
+        W, L, H, dk, dv, r, ff, V = DECODER_SIZES[size]
+        model = loaders.get_decoder_lm(None, cfg, device=device, synth_seed=11)
+        res = {"config": {"width": W, "layers": L, "heads": H, "dim": dk, "vdim": dv, "kv_rank": r, "ff": ff, "vocab": V}}
+        # ---- prefill: one request, T tokens on an empty slot (released between iterations)
+        gen = DecoderLMGen(model, slots=B, capacity=ctx + 64, max_step_tokens=max(T, B), max_want=B)
+        prompt = torch.randint(0, V, (T,), generator=g).tolist()
+
+        def prefill():
+            gen.step([(0, prompt)], [T - 1])
+            gen.release(0)
+        ms = _timed_steps(prefill, args.steps, args.warmup)
+        gen.set_option("time_kernels", 1)
+        gen.kernel_times()
+        for _ in range(3):
+            prefill()
+        kt = {k: v / 3 for k, v in gen.kernel_times().items()}
+        gen.set_option("time_kernels", 0)
+        fl = model.algorithmic_flops(T, 0)
+        attn_fl = 4 * H * r * T * (T + 1) // 2 * L
+        fold_fl = 2 * T * H * r * (dk + dv) * L
+        lin_fl = fl - attn_fl - fold_fl
+        res["prefill"] = {"ms": ms, "tokens_per_s": T / ms * 1e3, "tflops": fl / ms / 1e9, "frac_of_bf16_peak": fl / ms / 1e9 / tf,
+                          "kernel_ms": kt,
+                          "kernel_frac_of_bf16_peak": {"linear": lin_fl / kt["linear"] / 1e9 / tf, "attention": attn_fl / kt["attention"] / 1e9 / tf,
+                                                       "fold": fold_fl / kt["fold"] / 1e9 / tf}}
+        # ---- decode: B requests hold ctx tokens each, every step appends one token per request
+        filler = torch.randint(0, V, (ctx,), generator=g).tolist()
+        for b in range(B):
+            for a in range(0, ctx, max(T, B)):
+                gen.step([(b, filler[a:a + max(T, B)])], [])
+        toks = torch.randint(0, V, (B,), generator=g).tolist()
+        state = {"n": 0}
+
+        def decode():
+            if state["n"] >= 60:                       # stay inside the slots' capacity: drop the decoded tail and refill is not needed,
+                raise RuntimeError("decode loop longer than the spare capacity")
+            gen.step([(b, [toks[b]]) for b in range(B)], list(range(B)))
+            state["n"] += 1
+        n_dec = min(args.steps, 40)
+        ms = _timed_steps(decode, n_dec, min(args.warmup, 5))
+        gen.set_option("time_kernels", 1)
+        gen.kernel_times()
+        for _ in range(3):
+            decode()
+        kt = {k: v / 3 for k, v in gen.kernel_times().items()}
+        gen.set_option("time_kernels", 0)
+        nbytes = model.algorithmic_bytes(B, B * ctx)
+        attn_bytes = B * ctx * r * 2 * L
+        lin_bytes = nbytes - attn_bytes - 2 * H * r * (dk + dv) * L
+        res["decode"] = {"ms": ms, "tokens_per_s": B / ms * 1e3, "algorithmic_bytes": nbytes, "frac_of_hbm_peak": nbytes / ms / 1e6 / hbm,
+                         "kernel_ms": kt,
+                         "kernel_frac_of_hbm_peak": {"linear": lin_bytes / kt["linear"] / 1e6 / hbm, "attention": attn_bytes / kt["attention"] / 1e6 / hbm}}
+        gen.close()
+        del gen, model
+        torch.cuda.empty_cache()
+        # ---- the closest existing model: Moshi's temporal transformer at the same width / depth / batch / history
+        mcfg = LMConfig(dim=W, num_heads=W // 128, num_layers=L, text_card=V, n_q=8, dep_q=0, context=ctx + 64,
+                        delays=[0] * 9, depformer_dim=128, depformer_num_heads=1, depformer_num_layers=1, depformer_dim_feedforward=512)
+        lm = loaders.get_moshi_lm(None, lm_kwargs=mcfg.to_reference_kwargs(), device=device, synth_device=device)
+        mg = LMGen(lm, use_sampling=False)
+        codes = torch.randint(0, mcfg.card, (B, 8, 1), generator=g).to(device)
+        with mg.streaming(B):
+            mg.assume_fill(ctx)
+            ms = _timed_steps(lambda: mg.step(codes), n_dec, min(args.warmup, 5))
+            mb = mg.algorithmic_bytes(ctx)
+        res["moshi_temporal_decode"] = {"ms": ms, "tokens_per_s": B / ms * 1e3, "algorithmic_bytes": mb, "frac_of_hbm_peak": mb / ms / 1e6 / hbm,
+                                        "config": {"dim": W, "heads": W // 128, "layers": L, "ffn_hidden": mcfg.ffn_hidden, "kv_bytes_per_token_per_layer": 2 * W * 2,
+                                                   "latent_bytes_per_token_per_layer": r * 2}}
+        # its attention kernel alone (ring attention over K and V: the like kernel of the latent attention)
+        Hm, cap = W // 128, ctx + 64
+        k = torch.empty(B, Hm, cap, 128, device=device, dtype=torch.bfloat16).normal_()
+        v = torch.empty(B, Hm, cap, 128, device=device, dtype=torch.bfloat16).normal_()
+        qkv = torch.randn(B, 3 * Hm * 128, device=device).bfloat16()
+        o = torch.empty(B, Hm * 128, device=device, dtype=torch.bfloat16)
+        offs = torch.full((B,), ctx - 1, dtype=torch.int64, device=device)
+        mask = torch.ones(B, dtype=torch.bool, device=device)
+        stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+        ams = _event_time(lambda: _lib.check(_lib.lib().b200_op_attn_step(_lib.ptr(qkv), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(offs),
+                                                                          _lib.ptr(mask), B, Hm, cap, 0, 10000.0, stream)))
+        ab = 2 * B * Hm * ctx * 128 * 2
+        res["moshi_temporal_decode"]["attention_kernel"] = {"ms": ams, "algorithmic_bytes": ab, "frac_of_hbm_peak": ab / ams / 1e6 / hbm}
+        del lm, mg, k, v
+        torch.cuda.empty_cache()
+        out["sizes"][size] = res
+    out["gpu_launches"] = int(_lib.lib().b200_launch_count() - launches0)
+    print(json.dumps(out))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -559,7 +699,17 @@ def main() -> None:
                     help="storage of the temporal KV rings; fp8_e4m3 / int8 are opt-in extensions outside the reference's numerics "
                          "(half the ring, twice the sessions per GPU; logit error in tests/test_gpu_zv_kv_q8.py)")
     ap.add_argument("--quantize", action="store_true", help="BASELINE config 5: int8 (W8A8 QLinear) Moshi 7B instead of bf16")
+    ap.add_argument("--decoder-lm", action="store_true",
+                    help="instead of the default workload: prefill / decode throughput of the text-only decoder LM (Likosun design, random "
+                         "weights) beside the Moshi temporal transformer at equal width and depth; prints its own JSON line")
+    ap.add_argument("--decoder-sizes", default="w2048,w4096", help="comma-separated names out of " + ",".join(DECODER_SIZES))
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--decode-batch", type=int, default=32)
+    ap.add_argument("--context", type=int, default=2048)
     args = ap.parse_args()
+    if args.decoder_lm:
+        decoder_lm_arm(args)
+        return
     if args.impl == "reference":
         reference_arm(args)
     else:

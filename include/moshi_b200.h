@@ -363,11 +363,18 @@ int b200_dlm_load_tensor(b200_dlm* h, const char* name, const void* data_dev, in
 int b200_dlm_finalize(b200_dlm* h);
 int b200_dlm_destroy(b200_dlm* h);
 /* Allocates the latent cache ([slots][capacity][kv_rank] per layer) and the step buffers (up to max_step_tokens new tokens
- * and max_want logit rows per step).  use_tc = 1: bf16 linears of eligible shapes run on the LM's tcgen05 GEMM. */
+ * and max_want logit rows per step). */
 int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_tokens, int max_want, void* stream);
 int b200_dlm_cache_end(b200_dlm* h);
 int b200_dlm_set_stream(b200_dlm* h, void* stream);
-int b200_dlm_set_option(b200_dlm* h, const char* name, int value);   /* "use_tc", "trace_layers", "attn_split" */
+/* "use_tc" (before finalize; 1 = bf16 linears of eligible shapes on the LM's tcgen05 GEMM), "trace_layers" (before cache_begin),
+ * "attn_split" (CTAs per attention tile along the keys; 0 = chosen per step), "attn_tc" (0: latent attention on the CUDA
+ * cores also where the tensor-core kernel would take it), "time_kernels" (CUDA events around every
+ * operation, summed per class: a step then waits for its own end). */
+int b200_dlm_set_option(b200_dlm* h, const char* name, int value);
+/* Milliseconds spent so far per class of operation under "time_kernels": [0] linears, [1] latent attention, [2] the per-head
+ * folds around it (query through W_uk, sum through W_uv), [3] element-wise and norm kernels. */
+int b200_dlm_read_timers(b200_dlm* h, double* ms4_host, int reset);
 /* Gives a slot back: its length becomes 0 (the next request that gets the slot starts at position 0). */
 int b200_dlm_release(b200_dlm* h, int slot);
 int b200_dlm_slot_length(b200_dlm* h, int slot);
@@ -376,8 +383,8 @@ int b200_dlm_slot_length(b200_dlm* h, int slot);
  * Host arrays are int32.  Enqueues on the stream; does not synchronise. */
 int b200_dlm_step(b200_dlm* h, int n_entries, const int32_t* slots_host, const int32_t* counts_host,
                   const int32_t* tokens_host, int n_want, const int32_t* want_host, float* logits_dev);
-/* Samples one token per logit row of the last step with the LM's sampler (b200_op_sample): noise f32 [n_want][min(top_k, vocab)]
- * Exp(1) draws or NULL when use_sampling = 0 (greedy, first maximum). */
+/* One token per logit row of the last step.  use_sampling = 0 or temp <= 0: the first maximum of the fp32 logits.  Otherwise the
+ * LM's sampler (b200_op_sample) on their bf16 rounding: noise f32 [n_want][min(top_k, vocab)] Exp(1) draws. */
 int b200_dlm_sample(b200_dlm* h, const float* noise_dev, int use_sampling, float temp, int top_k, int64_t* out_dev);
 /* Debug / test hand-offs of the last step, copied device-to-device: "layers" f32 [n_layers][tokens][width] (needs option
  * trace_layers = 1: what each layer hands on), "logits" f32 [n_want][vocab]. */
@@ -452,6 +459,13 @@ int b200_op_attn_step(const void* qkv_dev, void* k_dev, void* v_dev, void* out_d
 int b200_op_attn_step_q8(const void* qkv_dev, void* k8_dev, void* v8_dev, float* ks_dev, float* vs_dev, void* out_dev,
                          const int64_t* pos_dev, const uint8_t* exec_mask_dev, int B, int H, int cap, int nsplit, float max_period,
                          int kv_dtype, void* stream);
+/* The decoder LM's latent attention kernel alone, for one request: qa f32 [T][H][r] (queries already folded through W_uk and
+ * the score scale), latents [ctx][r] (dtype B200_F32 or B200_BF16) with ctx = pos0 + T, sink f32 [H]; query t sits at position
+ * pos0 + t and sees keys 0 .. pos0 + t; out f32 [T][H][r] = sum_j p_j c_j with softmax denominators that also hold exp(sink[h]).
+ * nsplit > 1 cuts the keys over that many CTAs per tile (0 = the handle's own choice).  tensor_cores = 1: bf16 latents of
+ * 64, 128, .., 512 elements take the mma kernel (as in the handle); 0: always the CUDA-core kernel.  Synchronises (test helper). */
+int b200_op_latent_attention(const float* qa_dev, const void* latents_dev, int dtype, const float* sink_dev, float* out_dev,
+                             int T, int H, int r, int pos0, int nsplit, int tensor_cores, void* stream);
 int b200_op_sample(const void* logits_bf16_dev, const float* noise_dev, int64_t* out_dev, int B,
                    int card, int use_sampling, float temp, int top_k, void* stream);
 

@@ -133,6 +133,7 @@ _PROTOTYPES: dict[str, tuple[tp.Any, list]] = {
     "b200_dlm_step": (_I, [_P, _I, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32), _I, C.POINTER(C.c_int32), _P]),
     "b200_dlm_sample": (_I, [_P, _P, _I, C.c_float, _I, _P]),
     "b200_dlm_read_buffer": (_I, [_P, C.c_char_p, _P, C.c_int64, C.POINTER(C.c_int64)]),
+    "b200_dlm_read_timers": (_I, [_P, C.POINTER(C.c_double), _I]),
     "b200_dlm_algorithmic_bytes": (C.c_int64, [_P, _I, _I]),
     "b200_dlm_algorithmic_flops": (C.c_int64, [_P, _I, _I]),
     # one frame for every session slot, host buffers
@@ -156,6 +157,7 @@ _PROTOTYPES: dict[str, tuple[tp.Any, list]] = {
     "b200_op_tc_conv1d": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P]),
     "b200_op_attn_step": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, C.c_float, _P]),
     "b200_op_attn_step_q8": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, C.c_float, _I, _P]),
+    "b200_op_latent_attention": (_I, [_P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "b200_op_sample": (_I, [_P, _P, _P, _I, _I, _I, C.c_float, _I, _P]),
 }
 

@@ -45,7 +45,11 @@ struct b200_dlm {
   Arena weights, state;
   bool finalized = false, f32 = false;
   int device = -1;
-  int use_tc = 1, trace_layers = 0, attn_split = 0;
+  int use_tc = 1, trace_layers = 0, attn_split = 0, attn_tc = 1;
+  // option "time_kernels": CUDA events around every operation of a step, summed per class (bench.py's per-kernel roofline)
+  int time_kernels = 0;
+  std::vector<cudaEvent_t> ev_pool; std::vector<int> ev_class; size_t ev_used = 0;
+  double class_ms[4] = {0, 0, 0, 0};
   void *embed = nullptr;
   Weight head;
   float *fnw = nullptr, *fnb = nullptr;
@@ -132,6 +136,20 @@ int gemm_nt(cudaStream_t st, const TA* A, long long lda, long long sa, const TB*
   return check_launch("gemm_nt");
 }
 
+// the per-head products around the latent attention: tensor cores for bf16 weights (K a multiple of 16), else CUDA cores
+template <typename TA, typename TB, typename TC>
+int head_gemm(cudaStream_t st, const TA* A, long long lda, long long sa, const TB* B, long long ldb, long long sb, TC* C, long long ldc,
+              long long sc, int M, int N, int K, int batch, float alpha, bool tensor_cores) {
+  if constexpr (sizeof(TB) == 2) {
+    if (tensor_cores && K % 16 == 0) {
+      dim3 grid(ceil_div(N, 64), ceil_div(M, 64), batch);
+      B200_LAUNCH((gemm_nt_mma_kernel<TA, TC>), grid, 128, 0, st, A, lda, sa, B, ldb, sb, C, ldc, sc, M, N, K, alpha);
+      return check_launch("gemm_nt_mma");
+    }
+  }
+  return gemm_nt(st, A, lda, sa, B, ldb, sb, C, ldc, sc, M, N, K, batch, alpha);
+}
+
 // y[M][N] = x[M][K] . W^T in the compute type
 template <typename T>
 int linear(b200_dlm* h, const T* x, long long ldx, const Weight& w, T* y, long long ldy, int M);
@@ -157,44 +175,97 @@ int linear<bf16>(b200_dlm* h, const bf16* x, long long ldx, const Weight& w, bf1
 }
 
 template <typename T, int NCH, int RPW>
-int launch_attn(b200_dlm* h, const AttnParams& p, int tiles, int nsplit) {
+int launch_attn(cudaStream_t st, const AttnParams& p, int tiles, int nsplit) {
   const size_t smem = (size_t)32 * p.r * sizeof(T);
   static bool attr_set = false;
   if (!attr_set && smem > 48 * 1024) {
     B200_CUDA(cudaFuncSetAttribute(latent_attn_kernel<T, NCH, RPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attr_set = true;
   }
-  B200_LAUNCH((latent_attn_kernel<T, NCH, RPW>), dim3(tiles, nsplit), 128, smem, h->stream, p);
+  B200_LAUNCH((latent_attn_kernel<T, NCH, RPW>), dim3(tiles, nsplit), 128, smem, st, p);
   return check_launch("latent_attn");
+}
+
+// keys are cut over `nsplit` CTAs per tile when the tiles alone cannot fill the GPU (decoding, short portions)
+int pick_split(int forced, int tiles, int max_ctx, int rpt, int r, size_t part_floats) {
+  const int key_tiles = ceil_div(max_ctx, 32);
+  int nsplit = 1;
+  if (forced > 0) nsplit = forced;
+  else if (tiles < 148) nsplit = std::min(std::max(444 / tiles, 1), 64);      // one wave of three CTAs per SM
+  nsplit = std::max(1, std::min(nsplit, key_tiles));
+  nsplit = ceil_div(key_tiles, ceil_div(key_tiles, nsplit));                   // no split without a key tile
+  while (nsplit > 1 && (size_t)tiles * nsplit * rpt * (r + 2) > part_floats) --nsplit;
+  return nsplit;
+}
+
+template <int NKS>
+int launch_attn_mma(cudaStream_t st, const AttnParams& p, int tiles) {
+  const size_t smem = (size_t)2 * 32 * (p.r + 8) * 2 + (size_t)4 * 16 * 36 * 4;
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA(cudaFuncSetAttribute(latent_attn_mma_kernel<NKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+    attr_set = true;
+  }
+  B200_LAUNCH(latent_attn_mma_kernel<NKS>, dim3(tiles, p.nsplit), 128, smem, st, p);
+  return check_launch("latent_attn_mma");
+}
+
+// bf16 latents of 64, 128, .., 512 elements take the tensor-core kernel
+inline bool attn_mma_takes(int r, int rpt, bool bf16_latents) { return bf16_latents && rpt == 16 && r % 64 == 0 && r <= 512; }
+
+template <typename T>
+int run_attention(cudaStream_t st, AttnParams p, int tiles, int rpt, bool tensor_cores = true) {
+  const int r = p.r;
+  if (tensor_cores && attn_mma_takes(r, rpt, sizeof(T) == 2)) {
+    switch (r / 64) {
+      case 1: B200_TRY(launch_attn_mma<1>(st, p, tiles)); break;
+      case 2: B200_TRY(launch_attn_mma<2>(st, p, tiles)); break;
+      case 3: B200_TRY(launch_attn_mma<3>(st, p, tiles)); break;
+      case 4: B200_TRY(launch_attn_mma<4>(st, p, tiles)); break;
+      case 5: B200_TRY(launch_attn_mma<5>(st, p, tiles)); break;
+      case 6: B200_TRY(launch_attn_mma<6>(st, p, tiles)); break;
+      case 7: B200_TRY(launch_attn_mma<7>(st, p, tiles)); break;
+      default: B200_TRY(launch_attn_mma<8>(st, p, tiles)); break;
+    }
+  }
+  else if (r <= 64) B200_TRY((launch_attn<T, 2, 4>(st, p, tiles, p.nsplit)));
+  else if (r <= 128) B200_TRY((launch_attn<T, 4, 4>(st, p, tiles, p.nsplit)));
+  else if (r <= 256) B200_TRY((launch_attn<T, 8, 4>(st, p, tiles, p.nsplit)));
+  else if (r <= 512) B200_TRY((launch_attn<T, 16, 4>(st, p, tiles, p.nsplit)));
+  else B200_TRY((launch_attn<T, 32, 2>(st, p, tiles, p.nsplit)));
+  if (p.nsplit > 1) {
+    B200_LAUNCH(latent_attn_merge_kernel, dim3(tiles, ceil_div(rpt, 4)), 128, 0, st, p.part, p.tile_row0, p.tile_rows, p.out, r, p.nsplit, rpt);
+    B200_TRY(check_launch("latent_attn_merge"));
+  }
+  return B200_OK;
 }
 
 template <typename T>
 int attention(b200_dlm* h, const Layer& L, int max_ctx) {
   const TileSig& s = h->sigs[L.sig];
-  const int r = L.c.kv_rank;
   AttnParams p;
   p.qa = h->qa; p.cache = L.cache; p.sink = L.sink;
   p.tile_row0 = h->meta_dev + s.off_row0; p.tile_rows = h->meta_dev + s.off_rows; p.tile_slot = h->meta_dev + s.off_slot;
   p.tok_pos = h->meta_dev + h->off_pos;
-  p.out = h->ol; p.part = h->part; p.cap = h->cap; p.r = r; p.H = L.c.heads;
-  int nsplit = 1;
-  const int key_tiles = ceil_div(max_ctx, 32);
-  if (h->attn_split > 0) nsplit = h->attn_split;
-  else if (s.count < 148) nsplit = std::min(std::min(ceil_div(296, s.count), key_tiles), 64);
-  nsplit = std::max(1, std::min(nsplit, key_tiles));
-  while (nsplit > 1 && (size_t)s.count * nsplit * s.rpt * (r + 2) > h->part_floats) --nsplit;
-  p.nsplit = nsplit;
-  if (r <= 64) B200_TRY((launch_attn<T, 2, 4>(h, p, s.count, nsplit)));
-  else if (r <= 128) B200_TRY((launch_attn<T, 4, 4>(h, p, s.count, nsplit)));
-  else if (r <= 256) B200_TRY((launch_attn<T, 8, 4>(h, p, s.count, nsplit)));
-  else if (r <= 512) B200_TRY((launch_attn<T, 16, 4>(h, p, s.count, nsplit)));
-  else B200_TRY((launch_attn<T, 32, 2>(h, p, s.count, nsplit)));
-  if (nsplit > 1) {
-    B200_LAUNCH(latent_attn_merge_kernel, s.count, 128, 0, h->stream, h->part, p.tile_row0, p.tile_rows, h->ol, r, nsplit, s.rpt);
-    B200_TRY(check_launch("latent_attn_merge"));
+  p.out = h->ol; p.part = h->part; p.cap = h->cap; p.r = L.c.kv_rank; p.H = L.c.heads;
+  p.nsplit = pick_split(h->attn_split, s.count, max_ctx, s.rpt, p.r, h->part_floats);
+  return run_attention<T>(h->stream, p, s.count, s.rpt, h->attn_tc != 0);
+}
+
+enum { CLS_LINEAR = 0, CLS_ATTN = 1, CLS_FOLD = 2, CLS_ELEMENTWISE = 3 };
+
+int mark(b200_dlm* h, int cls) {       // cls >= 0 opens an interval of that class, -1 closes the open one
+  if (!h->time_kernels) return B200_OK;
+  if (h->ev_used == h->ev_pool.size()) {
+    cudaEvent_t e;
+    B200_CUDA(cudaEventCreate(&e));
+    h->ev_pool.push_back(e); h->ev_class.push_back(0);
   }
+  h->ev_class[h->ev_used] = cls;
+  B200_CUDA(cudaEventRecord(h->ev_pool[h->ev_used++], h->stream));
   return B200_OK;
 }
+#define TIMED(cls, ...) do { B200_TRY(mark(h, cls)); __VA_ARGS__; B200_TRY(mark(h, -1)); } while (0)
 
 template <typename T>
 int step_body(b200_dlm* h, int n_tok, int n_want, int max_ctx, float* logits_out) {
@@ -203,53 +274,53 @@ int step_body(b200_dlm* h, int n_tok, int n_want, int max_ctx, float* logits_out
   cudaStream_t st = h->stream;
   const int* meta = h->meta_dev;
   const long long stride = (long long)h->tmax * W;
-  B200_LAUNCH(embed_kernel<T>, n_tok, 256, 0, st, meta + h->off_tok, static_cast<const T*>(h->embed), c.vocab, W, c.embedding_scale,
-              h->xin, h->stack, h->err);
+  TIMED(CLS_ELEMENTWISE, B200_LAUNCH(embed_kernel<T>, n_tok, 256, 0, st, meta + h->off_tok, static_cast<const T*>(h->embed), c.vocab, W, c.embedding_scale,
+              h->xin, h->stack, h->err));
   T* hb = static_cast<T*>(h->hbuf);
-  B200_LAUNCH(layernorm_kernel<T>, n_tok, 256, 0, st, h->xin, (const int*)nullptr, h->layers[0].n1w, h->layers[0].n1b, hb, W, c.norm_eps);
+  TIMED(CLS_ELEMENTWISE, B200_LAUNCH(layernorm_kernel<T>, n_tok, 256, 0, st, h->xin, (const int*)nullptr, h->layers[0].n1w, h->layers[0].n1b, hb, W, c.norm_eps));
   for (int li = 0; li < c.n_layers; ++li) {
     const Layer& L = h->layers[li];
     const int H = L.c.heads, dk = L.c.dim, dv = L.c.vdim, r = L.c.kv_rank;
     T* proj = static_cast<T*>(h->proj);
-    B200_TRY(linear<T>(h, hb, W, L.cat, proj, L.ldp, n_tok));
+    TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, hb, W, L.cat, proj, L.ldp, n_tok)));
     // mixer: latent attention
-    B200_LAUNCH(latent_append_kernel<T>, ceil_div(n_tok, 4), 128, 0, st, proj, (long long)L.ldp, L.off_dkv, L.cnorm, static_cast<T*>(L.cache),
-                h->cap, r, meta + h->off_slot, meta + h->off_pos, n_tok, c.norm_eps);
+    TIMED(CLS_ELEMENTWISE, B200_LAUNCH(latent_append_kernel<T>, ceil_div(n_tok, 4), 128, 0, st, proj, (long long)L.ldp, L.off_dkv, L.cnorm, static_cast<T*>(L.cache),
+                h->cap, r, meta + h->off_slot, meta + h->off_pos, n_tok, c.norm_eps));
     // query folded through W_uk (and the score scale): qa[t][h][:] = scale * q[t][h][:] . W_uk[h]
-    B200_TRY(gemm_nt(st, proj + L.off_q, (long long)L.ldp, (long long)dk, static_cast<const T*>(L.ukT), (long long)dk, (long long)r * dk, h->qa,
-                     (long long)H * r, (long long)r, n_tok, r, dk, H, L.c.scale));
-    B200_TRY(attention<T>(h, L, max_ctx));
+    TIMED(CLS_FOLD, B200_TRY(head_gemm(st, proj + L.off_q, (long long)L.ldp, (long long)dk, static_cast<const T*>(L.ukT), (long long)dk, (long long)r * dk, h->qa,
+                     (long long)H * r, (long long)r, n_tok, r, dk, H, L.c.scale, h->attn_tc != 0)));
+    TIMED(CLS_ATTN, B200_TRY(attention<T>(h, L, max_ctx)));
     // values: o[t][h][:] = W_uv[h] . (sum_j p_j c_j)
     T* ob = static_cast<T*>(h->obuf);
-    B200_TRY(gemm_nt(st, h->ol, (long long)H * r, (long long)r, static_cast<const T*>(L.uv), (long long)r, (long long)dv * r, ob, (long long)H * dv,
-                     (long long)dv, n_tok, dv, r, H, 1.f));
+    TIMED(CLS_FOLD, B200_TRY(head_gemm(st, h->ol, (long long)H * r, (long long)r, static_cast<const T*>(L.uv), (long long)r, (long long)dv * r, ob, (long long)H * dv,
+                     (long long)dv, n_tok, dv, r, H, 1.f, h->attn_tc != 0)));
     T* mixo = static_cast<T*>(h->mixo);
-    B200_TRY(linear<T>(h, ob, (long long)H * dv, L.o, mixo, W, n_tok));
+    TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, ob, (long long)H * dv, L.o, mixo, W, n_tok)));
     // feed-forward
     T* ffo = nullptr;
     if (L.c.mlp == B200_MLP_DENSE_RELU2) {
       T* act = static_cast<T*>(h->act);
       const long long n = (long long)n_tok * L.c.ff;
-      B200_LAUNCH(relu2_kernel<T>, (unsigned)ceil_div64(n, 256), 256, 0, st, proj, (long long)L.ldp, L.off_up, act, L.c.ff, n);
+      TIMED(CLS_ELEMENTWISE, B200_LAUNCH(relu2_kernel<T>, (unsigned)ceil_div64(n, 256), 256, 0, st, proj, (long long)L.ldp, L.off_up, act, L.c.ff, n));
       ffo = static_cast<T*>(h->ffo);
-      B200_TRY(linear<T>(h, act, L.c.ff, L.down, ffo, W, n_tok));
+      TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, act, L.c.ff, L.down, ffo, W, n_tok)));
     }
     const bool last = li + 1 == c.n_layers;
-    B200_LAUNCH(block_end_kernel<T>, n_tok, 256, 0, st, h->xin, mixo, ffo, proj, (long long)L.ldp, L.off_g1, L.off_g2, L.b1, L.b2, c.residual_mult,
+    TIMED(CLS_ELEMENTWISE, B200_LAUNCH(block_end_kernel<T>, n_tok, 256, 0, st, h->xin, mixo, ffo, proj, (long long)L.ldp, L.off_g1, L.off_g2, L.b1, L.b2, c.residual_mult,
                 h->stack, stride, li, L.avg, h->trace_layers ? h->trace + (long long)li * stride : nullptr,
-                last ? nullptr : h->layers[li + 1].n1w, last ? nullptr : h->layers[li + 1].n1b, hb, W, c.norm_eps);
+                last ? nullptr : h->layers[li + 1].n1w, last ? nullptr : h->layers[li + 1].n1b, hb, W, c.norm_eps));
   }
   B200_TRY(check_launch("decoder LM layers"));
   if (n_want > 0) {
     T* hf = static_cast<T*>(h->hf);
-    B200_LAUNCH(layernorm_kernel<T>, n_want, 256, 0, st, h->xin, meta + h->off_want, h->fnw, h->fnb, hf, W, c.norm_eps);
+    TIMED(CLS_ELEMENTWISE, B200_LAUNCH(layernorm_kernel<T>, n_want, 256, 0, st, h->xin, meta + h->off_want, h->fnw, h->fnb, hf, W, c.norm_eps));
     if (h->head.tiles) {
       const int ldl = (c.vocab + 7) / 8 * 8;
-      B200_TRY(linear<bf16>(h, reinterpret_cast<const bf16*>(hf), W, h->head, h->head_bf, ldl, n_want));
+      TIMED(CLS_LINEAR, B200_TRY(linear<bf16>(h, reinterpret_cast<const bf16*>(hf), W, h->head, h->head_bf, ldl, n_want)));
       const long long n = (long long)n_want * c.vocab;
       B200_LAUNCH(rows_to_f32_kernel, (unsigned)ceil_div64(n, 256), 256, 0, st, h->head_bf, (long long)ldl, h->logits, c.vocab, n);
     } else {
-      B200_TRY(gemm_nt(st, hf, (long long)W, 0, static_cast<const T*>(h->head.rm), (long long)W, 0, h->logits, (long long)c.vocab, 0, n_want, c.vocab, W, 1, 1.f));
+      TIMED(CLS_LINEAR, B200_TRY(gemm_nt(st, hf, (long long)W, 0, static_cast<const T*>(h->head.rm), (long long)W, 0, h->logits, (long long)c.vocab, 0, n_want, c.vocab, W, 1, 1.f)));
     }
     if (logits_out)
       B200_CUDA(cudaMemcpyAsync(logits_out, h->logits, (size_t)n_want * c.vocab * 4, cudaMemcpyDeviceToDevice, st));
@@ -300,6 +371,10 @@ int b200_dlm_set_option(b200_dlm* h, const char* name, int value) {
   } else if (n == "trace_layers") {
     if (h->slots) B200_FAIL(B200_ERR_STATE, "dlm_set_option: trace_layers must be set before cache_begin");
     h->trace_layers = value != 0;
+  } else if (n == "attn_tc") {
+    h->attn_tc = value != 0;
+  } else if (n == "time_kernels") {
+    h->time_kernels = value != 0;
   } else if (n == "attn_split") {
     h->attn_split = value < 0 ? 0 : value;
   } else {
@@ -396,6 +471,8 @@ int b200_dlm_cache_end(b200_dlm* h) {
   if (h->slots) cudaStreamSynchronize(h->stream);
   h->state.free_all();
   if (h->meta_pin) { cudaFreeHost(h->meta_pin); h->meta_pin = nullptr; }
+  for (auto e : h->ev_pool) cudaEventDestroy(e);
+  h->ev_pool.clear(); h->ev_class.clear(); h->ev_used = 0;
   if (h->ev_meta) { cudaEventDestroy(h->ev_meta); h->ev_meta = nullptr; }
   h->plans.clear();
   h->slots = h->cap = h->tmax = h->wmax = 0;
@@ -541,6 +618,15 @@ int b200_dlm_step(b200_dlm* h, int n_entries, const int32_t* slots_host, const i
   B200_CUDA(cudaEventRecord(h->ev_meta, h->stream));
   const int rc = h->f32 ? step_body<float>(h, t, n_want, max_ctx, logits_dev) : step_body<bf16>(h, t, n_want, max_ctx, logits_dev);
   if (rc != B200_OK) return rc;
+  if (h->time_kernels && h->ev_used) {      // diagnostics only: waits for the step and sums its intervals per class
+    B200_CUDA(cudaStreamSynchronize(h->stream));
+    for (size_t i = 0; i + 1 < h->ev_used; i += 2) {
+      float ms = 0.f;
+      B200_CUDA(cudaEventElapsedTime(&ms, h->ev_pool[i], h->ev_pool[i + 1]));
+      h->class_ms[h->ev_class[i]] += ms;
+    }
+    h->ev_used = 0;
+  }
   for (int e = 0; e < n_entries; ++e) h->len[slots_host[e]] += counts_host[e];
   h->last_tokens = t; h->last_want = n_want;
   return B200_OK;
@@ -550,11 +636,15 @@ int b200_dlm_sample(b200_dlm* h, const float* noise_dev, int use_sampling, float
   using namespace b200::lm;
   if (!h || !h->slots || h->last_want < 1 || !out_dev) B200_FAIL(B200_ERR_STATE, "dlm_sample: the last step left no logits");
   const int V = h->cfg.vocab;
+  DeviceGuard g(h->device);
+  if (!use_sampling || temp <= 0.f) {        // greedy: on the fp32 logits, whatever the vocabulary's size
+    B200_LAUNCH(argmax_rows_kernel, h->last_want, 256, 0, h->stream, h->logits, V, reinterpret_cast<long long*>(out_dev));
+    return check_launch("dlm_sample (greedy)");
+  }
   if (V + 1 > 65535) B200_FAIL(B200_ERR_SHAPE, "dlm_sample: the sampler takes vocabularies up to 65534");
   if (top_k < 1) top_k = 1;
   if (top_k > SAMPLE_MAX_K) B200_FAIL(B200_ERR_SHAPE, "dlm_sample: top_k above %d", SAMPLE_MAX_K);
-  if (use_sampling && temp > 0.f && !noise_dev) B200_FAIL(B200_ERR_INVALID, "dlm_sample: sampling needs noise");
-  DeviceGuard g(h->device);
+  if (!noise_dev) B200_FAIL(B200_ERR_INVALID, "dlm_sample: sampling needs noise");
   const long long n = (long long)h->last_want * V;
   B200_LAUNCH(logits_to_bf16_kernel, (unsigned)ceil_div64(n, 256), 256, 0, h->stream, h->logits, h->logits_bf, n);
   const int k = top_k < V ? top_k : V;
@@ -597,6 +687,12 @@ int b200_dlm_read_buffer(b200_dlm* h, const char* name, void* dst_dev, int64_t c
   B200_FAIL(B200_ERR_INVALID, "dlm_read_buffer: unknown buffer '%s'", name);
 }
 
+int b200_dlm_read_timers(b200_dlm* h, double* ms4_host, int reset) {
+  if (!h || !ms4_host) B200_FAIL(B200_ERR_INVALID, "dlm_read_timers: null argument");
+  for (int i = 0; i < 4; ++i) { ms4_host[i] = h->class_ms[i]; if (reset) h->class_ms[i] = 0; }
+  return B200_OK;
+}
+
 // weights once + the cached latents the new tokens read + the latents they write
 int64_t b200_dlm_algorithmic_bytes(b200_dlm* h, int tokens, int context) {
   if (!h) return 0;
@@ -617,6 +713,34 @@ int64_t b200_dlm_algorithmic_flops(b200_dlm* h, int tokens, int context) {
     f += 4 * H * r * (T * context + T * (T + 1) / 2);
   }
   return f + 2 * T * W * h->cfg.vocab;
+}
+
+int b200_op_latent_attention(const float* qa_dev, const void* latents_dev, int dtype, const float* sink_dev, float* out_dev,
+                             int T, int H, int r, int pos0, int nsplit, int tensor_cores, void* stream) {
+  if (!qa_dev || !latents_dev || !sink_dev || !out_dev) B200_FAIL(B200_ERR_INVALID, "op_latent_attention: null pointer");
+  if (T < 1 || H < 1 || r < 1 || r > 1024 || pos0 < 0) B200_FAIL(B200_ERR_SHAPE, "op_latent_attention: bad shape");
+  if (dtype != B200_F32 && dtype != B200_BF16) B200_FAIL(B200_ERR_INVALID, "op_latent_attention: latents must be f32 or bf16");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int rpt = rows_per_tile(r), rows = T * H, tiles = ceil_div(rows, rpt);
+  std::vector<int> meta((size_t)3 * tiles + T);
+  for (int i = 0; i < tiles; ++i) { meta[i] = i * rpt; meta[tiles + i] = std::min(rpt, rows - i * rpt); meta[2 * tiles + i] = 0; }
+  for (int t = 0; t < T; ++t) meta[3 * tiles + t] = pos0 + t;
+  int* meta_dev = nullptr; float* part = nullptr;
+  B200_CUDA(cudaMalloc(&meta_dev, meta.size() * sizeof(int)));
+  B200_CUDA(cudaMemcpyAsync(meta_dev, meta.data(), meta.size() * sizeof(int), cudaMemcpyHostToDevice, st));
+  AttnParams p;
+  p.qa = qa_dev; p.cache = latents_dev; p.sink = sink_dev; p.tile_row0 = meta_dev; p.tile_rows = meta_dev + tiles; p.tile_slot = meta_dev + 2 * tiles;
+  p.tok_pos = meta_dev + 3 * tiles; p.out = out_dev; p.cap = pos0 + T; p.r = r; p.H = H;
+  const size_t part_floats = (size_t)600 * 16 * (r + 2);
+  p.nsplit = pick_split(nsplit, tiles, pos0 + T, rpt, r, nsplit > 0 ? (size_t)tiles * nsplit * rpt * (r + 2) : part_floats);
+  const size_t need = (size_t)tiles * p.nsplit * rpt * (r + 2);
+  B200_CUDA(cudaMalloc(&part, std::max(need, (size_t)1) * sizeof(float)));
+  p.part = part;
+  int rc = dtype == B200_F32 ? run_attention<float>(st, p, tiles, rpt) : run_attention<bf16>(st, p, tiles, rpt, tensor_cores != 0);
+  cudaError_t e = cudaStreamSynchronize(st);
+  cudaFree(meta_dev); cudaFree(part);
+  if (rc == B200_OK && e != cudaSuccess) { set_error("op_latent_attention: %s", cudaGetErrorString(e)); rc = B200_ERR_CUDA; }
+  return rc;
 }
 
 }  // extern "C"

@@ -363,26 +363,303 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(AttnParams p) {
   }
 }
 
-// merges the splits of one row: out = sum_s o_s exp(m_s - M) / sum_s l_s exp(m_s - M); one warp per row
+// ---------------------------------------------------------------------------------------------------------------------------
+// The same attention on the tensor cores, for bf16 latents whose size is a multiple of 64 (<= 512): both products of a 16-row
+// tile against a 32-key tile run as mma.sync m16n8k16 (bf16 in, fp32 accumulate).  The CTA's four warps cut the LATENT axis:
+// warp w owns elements [w * r/4, (w + 1) * r/4) of every latent, for the scores (a partial dot over its share, summed over
+// the warps through shared memory) as well as for the weighted sum (its share of the output columns), so that the query
+// fragments and the output accumulators stay in registers and every warp reads only its own columns of the key tile.
+// The softmax (fp32, with the sink) is done by every warp on the summed scores; the weights enter the second product as bf16.
+// Key tiles are double-buffered with cp.async; rows of the tile beyond the last key are zero-filled.
+// ---------------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem_row) {
+  const unsigned addr = (unsigned)__cvta_generic_to_shared(smem_row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem_row) {
+  const unsigned addr = (unsigned)__cvta_generic_to_shared(smem_row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+template <int NKS>      // 16-element steps of a warp's share of the latent: r = 64 * NKS
+__global__ void __launch_bounds__(128) latent_attn_mma_kernel(AttnParams p) {
+  constexpr int KT = 32, R = 64 * NKS, SL = 16 * NKS, STRIDE = R + 8, SPS = 36;     // r = 512: 74 KB per CTA, three CTAs per SM
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* cs = reinterpret_cast<bf16*>(smem_raw);                                     // [2][KT][STRIDE]
+  float* sp = reinterpret_cast<float*>(smem_raw + (size_t)2 * KT * STRIDE * 2);     // [4 warps][16][SPS] partial scores
+  const int tile = blockIdx.x, split = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+  const int H = p.H;
+  const int row0 = p.tile_row0[tile], nrows = p.tile_rows[tile];
+  const bf16* cbase = static_cast<const bf16*>(p.cache) + (long long)p.tile_slot[tile] * p.cap * R;
+  const int kmax = p.tok_pos[(row0 + nrows - 1) / H];
+  const int n_kt = kmax / KT + 1;
+  const int per = (n_kt + p.nsplit - 1) / p.nsplit;
+  const int kt0 = split * per, kt1 = min(n_kt, kt0 + per);
+  const int col0 = warp * SL;
+
+  // rows g and g + 8 of the tile
+  int pos[2]; float m[2], l[2];
+  unsigned qf[NKS][4];
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    const int lr = g + 8 * hf;
+    const bool valid = lr < nrows;
+    const int gr = row0 + (valid ? lr : 0);
+    pos[hf] = valid ? p.tok_pos[gr / H] : -1;
+    if (valid && split == 0) { m[hf] = p.sink[gr % H]; l[hf] = t4 == 0 ? 1.f : 0.f; }
+    else { m[hf] = valid ? -INFINITY : 0.f; l[hf] = 0.f; }
+    const float* qrow = p.qa + (long long)gr * R + col0;
+#pragma unroll
+    for (int ks = 0; ks < NKS; ++ks) {
+      const float2 a = valid ? *reinterpret_cast<const float2*>(qrow + ks * 16 + 2 * t4) : make_float2(0.f, 0.f);
+      const float2 b = valid ? *reinterpret_cast<const float2*>(qrow + ks * 16 + 2 * t4 + 8) : make_float2(0.f, 0.f);
+      qf[ks][hf] = pack_bf16(a.x, a.y);
+      qf[ks][2 + hf] = pack_bf16(b.x, b.y);
+    }
+  }
+  float oacc[2 * NKS][4];
+#pragma unroll
+  for (int i = 0; i < 2 * NKS; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
+
+  auto stage = [&](int kt, int buf) {
+    const int j0 = kt * KT, nk = min(KT, kmax + 1 - j0);
+    constexpr int CPR = R / 8;                                   // 16-byte chunks per key
+    bf16* dst = cs + (size_t)buf * KT * STRIDE;
+    const bf16* src = cbase + (long long)j0 * R;
+    for (int c = threadIdx.x; c < KT * CPR; c += 128) {
+      const int row = c / CPR, cc = c - row * CPR;
+      bf16* d = dst + row * STRIDE + cc * 8;
+      if (row < nk) {
+        const unsigned sa = (unsigned)__cvta_generic_to_shared(d);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(src + (long long)row * R + cc * 8));
+      } else {
+        *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+
+  if (kt0 < kt1) stage(kt0, 0);
+  for (int kt = kt0; kt < kt1; ++kt) {
+    const int buf = (kt - kt0) & 1;
+    asm volatile("cp.async.wait_group 0;\n" ::);
+    __syncthreads();
+    if (kt + 1 < kt1) stage(kt + 1, buf ^ 1);
+    const bf16* ct = cs + (size_t)buf * KT * STRIDE;
+    // partial scores of this warp's share of the latent: [16 rows][32 keys]
+    float sacc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f; }
+#pragma unroll
+    for (int ks = 0; ks < NKS; ++ks) {
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {
+        unsigned b[4];
+        const int mi = lane >> 3;
+        ldmatrix_x4(b, ct + (np * 16 + (mi >> 1) * 8 + (lane & 7)) * STRIDE + col0 + ks * 16 + (mi & 1) * 8);
+        mma_bf16_16816(sacc[2 * np], qf[ks], b[0], b[1]);
+        mma_bf16_16816(sacc[2 * np + 1], qf[ks], b[2], b[3]);
+      }
+    }
+    float* mine = sp + warp * 16 * SPS;
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) {
+      *reinterpret_cast<float2*>(mine + g * SPS + nb * 8 + 2 * t4) = make_float2(sacc[nb][0], sacc[nb][1]);
+      *reinterpret_cast<float2*>(mine + (g + 8) * SPS + nb * 8 + 2 * t4) = make_float2(sacc[nb][2], sacc[nb][3]);
+    }
+    __syncthreads();
+    // softmax update of rows g, g + 8 on the summed scores; this thread holds keys {2t, 2t+1} + 8 * q, q = 0..3
+    const int j0 = kt * KT;
+    unsigned pf[2][4];
+    float corr[2];
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      float s[8];
+      const int lr = g + 8 * hf;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const float2 v = *reinterpret_cast<const float2*>(sp + (w * 16 + lr) * SPS + q * 8 + 2 * t4);
+          acc.x += v.x; acc.y += v.y;
+        }
+        const int key = j0 + q * 8 + 2 * t4;
+        s[2 * q] = key <= pos[hf] ? acc.x : -INFINITY;
+        s[2 * q + 1] = key + 1 <= pos[hf] ? acc.y : -INFINITY;
+      }
+      float mx = s[0];
+#pragma unroll
+      for (int i = 1; i < 8; ++i) mx = fmaxf(mx, s[i]);
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float mn = fmaxf(m[hf], mx);
+      const float mu = mn == -INFINITY ? 0.f : mn;
+      corr[hf] = __expf(m[hf] - mu);                 // m = -inf -> 0 (nothing accumulated yet)
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { s[i] = __expf(s[i] - mu); sum += s[i]; }
+      l[hf] = l[hf] * corr[hf] + sum;
+      m[hf] = mn;
+      // A fragments of the weights: k-step 0 = keys 0..15 (q = 0, 1), k-step 1 = keys 16..31 (q = 2, 3)
+      pf[0][hf] = pack_bf16(s[0], s[1]); pf[0][2 + hf] = pack_bf16(s[2], s[3]);
+      pf[1][hf] = pack_bf16(s[4], s[5]); pf[1][2 + hf] = pack_bf16(s[6], s[7]);
+    }
+#pragma unroll
+    for (int i = 0; i < 2 * NKS; ++i) { oacc[i][0] *= corr[0]; oacc[i][1] *= corr[0]; oacc[i][2] *= corr[1]; oacc[i][3] *= corr[1]; }
+    // weighted sum over this warp's output columns
+#pragma unroll
+    for (int k2 = 0; k2 < 2; ++k2) {
+#pragma unroll
+      for (int np = 0; np < NKS; ++np) {
+        unsigned b[4];
+        const int mi = lane >> 3;
+        ldmatrix_x4_trans(b, ct + (k2 * 16 + (mi & 1) * 8 + (lane & 7)) * STRIDE + col0 + np * 16 + (mi >> 1) * 8);
+        mma_bf16_16816(oacc[2 * np], pf[k2], b[0], b[1]);
+        mma_bf16_16816(oacc[2 * np + 1], pf[k2], b[2], b[3]);
+      }
+    }
+  }
+
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    const int lr = g + 8 * hf;
+    float lt = l[hf];
+    lt += __shfl_xor_sync(0xffffffffu, lt, 1);
+    lt += __shfl_xor_sync(0xffffffffu, lt, 2);
+    if (lr >= nrows) continue;
+    if (p.nsplit == 1) {
+      const float inv = 1.f / lt;
+      float* dst = p.out + (long long)(row0 + lr) * R + col0;
+#pragma unroll
+      for (int nb = 0; nb < 2 * NKS; ++nb)
+        *reinterpret_cast<float2*>(dst + nb * 8 + 2 * t4) = make_float2(oacc[nb][2 * hf] * inv, oacc[nb][2 * hf + 1] * inv);
+    } else {
+      float* dst = p.part + (((long long)tile * p.nsplit + split) * 16 + lr) * (R + 2);
+#pragma unroll
+      for (int nb = 0; nb < 2 * NKS; ++nb)
+        *reinterpret_cast<float2*>(dst + col0 + nb * 8 + 2 * t4) = make_float2(oacc[nb][2 * hf], oacc[nb][2 * hf + 1]);
+      if (warp == 0 && t4 == 0) { dst[R] = m[hf]; dst[R + 1] = lt; }
+    }
+  }
+}
+
+// merges the splits of one row: out = sum_s o_s exp(m_s - M) / sum_s l_s exp(m_s - M); one warp per row, grid (tiles, rows / 4).
+// The split weights are computed once per row (lane s owns splits s and s + 32), then every output element is a short sum of
+// independent loads.
 __global__ void __launch_bounds__(128) latent_attn_merge_kernel(const float* __restrict__ part, const int* __restrict__ tile_row0,
                                                                 const int* __restrict__ tile_rows, float* __restrict__ out, int r,
                                                                 int nsplit, int rows_per_tile) {
-  const int tile = blockIdx.x, lane = threadIdx.x & 31;
-  for (int lr = threadIdx.x >> 5; lr < tile_rows[tile]; lr += 4) {
-    const float* base = part + ((long long)tile * nsplit * rows_per_tile + lr) * (r + 2);
-    const long long ss = (long long)rows_per_tile * (r + 2);
-    float M = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, base[s * ss + r]);
-    float L = 0.f;
-    for (int s = 0; s < nsplit; ++s) { const float ms = base[s * ss + r]; if (ms > -INFINITY) L += base[s * ss + r + 1] * expf(ms - M); }
-    const float inv = 1.f / L;
-    float* dst = out + (long long)(tile_row0[tile] + lr) * r;
-    for (int e = lane; e < r; e += 32) {
-      float acc = 0.f;
-      for (int s = 0; s < nsplit; ++s) { const float ms = base[s * ss + r]; if (ms > -INFINITY) acc += base[s * ss + e] * expf(ms - M); }
-      dst[e] = acc * inv;
-    }
+  __shared__ float wsm[4][64];
+  const int tile = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int lr = blockIdx.y * 4 + warp;
+  if (lr >= tile_rows[tile]) return;
+  const float* base = part + ((long long)tile * nsplit * rows_per_tile + lr) * (r + 2);
+  const long long ss = (long long)rows_per_tile * (r + 2);
+  float ms[2], ls[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int s = lane + 32 * i;
+    ms[i] = s < nsplit ? base[s * ss + r] : -INFINITY;
+    ls[i] = s < nsplit ? base[s * ss + r + 1] : 0.f;
   }
+  const float M = warp_max(fmaxf(ms[0], ms[1]));
+  float L = 0.f;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const float w = ms[i] > -INFINITY ? expf(ms[i] - M) : 0.f;
+    wsm[warp][lane + 32 * i] = w;
+    L += ls[i] * w;
+  }
+  const float inv = 1.f / warp_sum(L);
+  __syncwarp();
+  float* dst = out + (long long)(tile_row0[tile] + lr) * r;
+  for (int e = lane; e < r; e += 32) {
+    float acc = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < nsplit; ++s) acc = fmaf(base[s * ss + e], wsm[warp][s], acc);
+    dst[e] = acc * inv;
+  }
+}
+
+// C[z][M][N] = alpha * A[z][M][K] . B[z][N][K]^T on the tensor cores (mma.sync m16n8k16, bf16 in, fp32 accumulate) for the
+// per-head products around the latent attention in bfloat16: A is bf16 or fp32 (rounded to bf16 on its way into shared
+// memory), B bf16, C fp32 or bf16.  K a multiple of 16; M and N are free (zero-filled edges).  CTA tile 64 x 64, 4 warps of
+// 16 rows x 64 columns, 32-element k-steps through shared memory.
+template <typename TA, typename TC>
+__global__ void __launch_bounds__(128) gemm_nt_mma_kernel(const TA* __restrict__ A, long long lda, long long sa, const bf16* __restrict__ B,
+                                                          long long ldb, long long sb, TC* __restrict__ C, long long ldc, long long sc,
+                                                          int M, int N, int K, float alpha) {
+  constexpr int BM = 64, BN = 64, BK = 32, ST = BK + 8;
+  __shared__ __align__(16) bf16 As[BM][ST];
+  __shared__ __align__(16) bf16 Bs[BN][ST];
+  A += (long long)blockIdx.z * sa; B += (long long)blockIdx.z * sb; C += (long long)blockIdx.z * sc;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+  // 64 rows x 32 k of each operand per step: 8 element pairs per thread, fetched into registers one step ahead
+  unsigned ra[8], rb[8];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = threadIdx.x + 128 * j;
+      const int rr = i / (BK / 2), kk = (i % (BK / 2)) * 2;
+      float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+      if (k0 + kk < K) {
+        if (m0 + rr < M) { a0 = to_f(A[(long long)(m0 + rr) * lda + k0 + kk]); a1 = to_f(A[(long long)(m0 + rr) * lda + k0 + kk + 1]); }
+        if (n0 + rr < N) { b0 = to_f(B[(long long)(n0 + rr) * ldb + k0 + kk]); b1 = to_f(B[(long long)(n0 + rr) * ldb + k0 + kk + 1]); }
+      }
+      ra[j] = pack_bf16(a0, a1); rb[j] = pack_bf16(b0, b1);
+    }
+  };
+  fetch(0);
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = threadIdx.x + 128 * j;
+      const int rr = i / (BK / 2), kk = (i % (BK / 2)) * 2;
+      *reinterpret_cast<unsigned*>(&As[rr][kk]) = ra[j];
+      *reinterpret_cast<unsigned*>(&Bs[rr][kk]) = rb[j];
+    }
+    __syncthreads();
+    if (k0 + BK < K) fetch(k0 + BK);
+#pragma unroll
+    for (int ks = 0; ks < BK / 16; ++ks) {
+      unsigned a[4];
+      const int mi = lane >> 3;
+      ldmatrix_x4(a, &As[warp * 16 + (mi & 1) * 8 + (lane & 7)][ks * 16 + (mi >> 1) * 8]);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        unsigned b[4];
+        ldmatrix_x4(b, &Bs[np * 16 + (mi >> 1) * 8 + (lane & 7)][ks * 16 + (mi & 1) * 8]);
+        mma_bf16_16816(acc[2 * np], a, b[0], b[1]);
+        mma_bf16_16816(acc[2 * np + 1], a, b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int m = m0 + warp * 16 + g + 8 * hf, n = n0 + nb * 8 + 2 * t4;
+      if (m < M) {
+        if (n < N) C[(long long)m * ldc + n] = from_f<TC>(alpha * acc[nb][2 * hf]);
+        if (n + 1 < N) C[(long long)m * ldc + n + 1] = from_f<TC>(alpha * acc[nb][2 * hf + 1]);
+      }
+    }
 }
 
 // bf16 rows with a padded stride -> fp32 [rows][V]
@@ -391,6 +668,26 @@ __global__ void rows_to_f32_kernel(const bf16* __restrict__ in, long long ld, fl
   if (i >= n) return;
   const long long row = i / V;
   out[i] = __bfloat162float(in[row * ld + (i - row * V)]);
+}
+
+// greedy choice on the fp32 logits themselves: first maximum of every row; one CTA per row
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ logits, int V, long long* __restrict__ out) {
+  __shared__ float bv[8];
+  __shared__ int bi[8];
+  const float* row = logits + (long long)blockIdx.x * V;
+  float best = -INFINITY; int idx = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += 256) { const float v = row[i]; if (v > best || (v == best && i < idx)) { best = v; idx = i; } }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o); const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
+    out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+  }
 }
 
 // logits f32 -> bf16 rows for the LM's sampler

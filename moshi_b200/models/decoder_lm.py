@@ -115,6 +115,12 @@ class DecoderLMGen:
     def set_option(self, name: str, value: int) -> None:
         _lib.check(self._lib.b200_dlm_set_option(self._h, name.encode(), int(value)))
 
+    def kernel_times(self, reset: bool = True) -> dict[str, float]:
+        """Milliseconds per class of operation since the last reset (needs ``set_option("time_kernels", 1)``)."""
+        ms = (C.c_double * 4)()
+        _lib.check(self._lib.b200_dlm_read_timers(self._h, ms, int(reset)))
+        return dict(zip(("linear", "attention", "fold", "elementwise"), (float(x) for x in ms)))
+
     def release(self, slot: int) -> None:
         """The slot's request is finished: what it holds is given back."""
         _lib.check(self._lib.b200_dlm_release(self._h, int(slot)))
