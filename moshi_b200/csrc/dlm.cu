@@ -141,7 +141,9 @@ template <typename TA, typename TB, typename TC>
 int head_gemm(cudaStream_t st, const TA* A, long long lda, long long sa, const TB* B, long long ldb, long long sb, TC* C, long long ldc,
               long long sc, int M, int N, int K, int batch, float alpha, bool tensor_cores) {
   if constexpr (sizeof(TB) == 2) {
-    if (tensor_cores && K % 16 == 0) {
+    constexpr long long AE = 16 / (long long)sizeof(TA);       // elements of A per 16 bytes
+    const bool aligned = lda % AE == 0 && sa % AE == 0 && ldb % 8 == 0 && sb % 8 == 0 && (uintptr_t)A % 16 == 0 && (uintptr_t)B % 16 == 0;
+    if (tensor_cores && K % 16 == 0 && aligned) {
       dim3 grid(ceil_div(N, 64), ceil_div(M, 64), batch);
       B200_LAUNCH((gemm_nt_mma_kernel<TA, TC>), grid, 128, 0, st, A, lda, sa, B, ldb, sb, C, ldc, sc, M, N, K, alpha);
       return check_launch("gemm_nt_mma");
@@ -190,8 +192,8 @@ int launch_attn(cudaStream_t st, const AttnParams& p, int tiles, int nsplit) {
 int pick_split(int forced, int tiles, int max_ctx, int rpt, int r, size_t part_floats) {
   const int key_tiles = ceil_div(max_ctx, 32);
   int nsplit = 1;
-  if (forced > 0) nsplit = forced;
-  else if (tiles < 148) nsplit = std::min(std::max(444 / tiles, 1), 64);      // one wave of three CTAs per SM
+  if (forced > 0) nsplit = std::min(forced, 64);
+  else if (tiles < 148) nsplit = std::min(std::max(296 / tiles, 1), 64);      // one wave of two CTAs per SM
   nsplit = std::max(1, std::min(nsplit, key_tiles));
   nsplit = ceil_div(key_tiles, ceil_div(key_tiles, nsplit));                   // no split without a key tile
   while (nsplit > 1 && (size_t)tiles * nsplit * rpt * (r + 2) > part_floats) --nsplit;
@@ -234,7 +236,7 @@ int run_attention(cudaStream_t st, AttnParams p, int tiles, int rpt, bool tensor
   else if (r <= 512) B200_TRY((launch_attn<T, 16, 4>(st, p, tiles, p.nsplit)));
   else B200_TRY((launch_attn<T, 32, 2>(st, p, tiles, p.nsplit)));
   if (p.nsplit > 1) {
-    B200_LAUNCH(latent_attn_merge_kernel, dim3(tiles, ceil_div(rpt, 4)), 128, 0, st, p.part, p.tile_row0, p.tile_rows, p.out, r, p.nsplit, rpt);
+    B200_LAUNCH(latent_attn_merge_kernel, dim3(tiles, rpt), 128, 0, st, p.part, p.tile_row0, p.tile_rows, p.out, r, p.nsplit, rpt);
     B200_TRY(check_launch("latent_attn_merge"));
   }
   return B200_OK;

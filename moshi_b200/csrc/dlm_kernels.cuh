@@ -554,19 +554,19 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(AttnParams p) {
   }
 }
 
-// merges the splits of one row: out = sum_s o_s exp(m_s - M) / sum_s l_s exp(m_s - M); one warp per row, grid (tiles, rows / 4).
-// The split weights are computed once per row (lane s owns splits s and s + 32), then every output element is a short sum of
-// independent loads.
+// merges the splits of one row: out = sum_s o_s exp(m_s - M) / sum_s l_s exp(m_s - M); one CTA per row, grid (tiles, rows).
+// Every warp computes the split weights (lane s owns splits s and s + 32); then a thread owns element pairs of the row and
+// sums them over the splits with independent 8-byte loads (scalar loads when the latent size is odd).
 __global__ void __launch_bounds__(128) latent_attn_merge_kernel(const float* __restrict__ part, const int* __restrict__ tile_row0,
                                                                 const int* __restrict__ tile_rows, float* __restrict__ out, int r,
                                                                 int nsplit, int rows_per_tile) {
-  __shared__ float wsm[4][64];
+  __shared__ float wsm[64];
   const int tile = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int lr = blockIdx.y * 4 + warp;
+  const int lr = blockIdx.y;
   if (lr >= tile_rows[tile]) return;
   const float* base = part + ((long long)tile * nsplit * rows_per_tile + lr) * (r + 2);
   const long long ss = (long long)rows_per_tile * (r + 2);
-  float ms[2], ls[2];
+  float ms[2], ls[2], w[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int s = lane + 32 * i;
@@ -577,18 +577,30 @@ __global__ void __launch_bounds__(128) latent_attn_merge_kernel(const float* __r
   float L = 0.f;
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    const float w = ms[i] > -INFINITY ? expf(ms[i] - M) : 0.f;
-    wsm[warp][lane + 32 * i] = w;
-    L += ls[i] * w;
+    w[i] = ms[i] > -INFINITY ? expf(ms[i] - M) : 0.f;
+    L += ls[i] * w[i];
   }
   const float inv = 1.f / warp_sum(L);
-  __syncwarp();
+  if (warp == 0) { wsm[lane] = w[0]; wsm[lane + 32] = w[1]; }
+  __syncthreads();
   float* dst = out + (long long)(tile_row0[tile] + lr) * r;
-  for (int e = lane; e < r; e += 32) {
-    float acc = 0.f;
-#pragma unroll 4
-    for (int s = 0; s < nsplit; ++s) acc = fmaf(base[s * ss + e], wsm[warp][s], acc);
-    dst[e] = acc * inv;
+  if ((r & 1) == 0) {       // rows of r + 2 floats start on 8-byte boundaries
+    for (int e = threadIdx.x * 2; e < r; e += 256) {
+      float2 acc = make_float2(0.f, 0.f);
+#pragma unroll 8
+      for (int s = 0; s < nsplit; ++s) {
+        const float2 v = *reinterpret_cast<const float2*>(base + s * ss + e);
+        acc.x = fmaf(v.x, wsm[s], acc.x); acc.y = fmaf(v.y, wsm[s], acc.y);
+      }
+      *reinterpret_cast<float2*>(dst + e) = make_float2(acc.x * inv, acc.y * inv);
+    }
+  } else {
+    for (int e = threadIdx.x; e < r; e += 128) {
+      float acc = 0.f;
+#pragma unroll 8
+      for (int s = 0; s < nsplit; ++s) acc = fmaf(base[s * ss + e], wsm[s], acc);
+      dst[e] = acc * inv;
+    }
   }
 }
 
@@ -609,29 +621,41 @@ __global__ void __launch_bounds__(128) gemm_nt_mma_kernel(const TA* __restrict__
   float acc[8][4];
 #pragma unroll
   for (int i = 0; i < 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
-  // 64 rows x 32 k of each operand per step: 8 element pairs per thread, fetched into registers one step ahead
-  unsigned ra[8], rb[8];
+  // 64 rows x 32 k of each operand per step, fetched with 16-byte loads into registers one step ahead (the launcher checks
+  // that K is a multiple of 16 and that rows start on 16-byte boundaries, so a chunk lies inside K or outside it as a whole)
+  constexpr int ACH = sizeof(TA) == 2 ? 2 : 4;        // chunks of A per thread: 8 bf16 or 4 floats each
+  uint4 ra[ACH], rb[2];
   auto fetch = [&](int k0) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int i = threadIdx.x + 128 * j;
-      const int rr = i / (BK / 2), kk = (i % (BK / 2)) * 2;
-      float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
-      if (k0 + kk < K) {
-        if (m0 + rr < M) { a0 = to_f(A[(long long)(m0 + rr) * lda + k0 + kk]); a1 = to_f(A[(long long)(m0 + rr) * lda + k0 + kk + 1]); }
-        if (n0 + rr < N) { b0 = to_f(B[(long long)(n0 + rr) * ldb + k0 + kk]); b1 = to_f(B[(long long)(n0 + rr) * ldb + k0 + kk + 1]); }
-      }
-      ra[j] = pack_bf16(a0, a1); rb[j] = pack_bf16(b0, b1);
+    for (int j = 0; j < ACH; ++j) {
+      const int c = threadIdx.x + 128 * j;
+      const int per_row = sizeof(TA) == 2 ? 4 : 8, el = sizeof(TA) == 2 ? 8 : 4;
+      const int rr = c / per_row, kk = (c % per_row) * el;
+      ra[j] = (m0 + rr < M && k0 + kk < K) ? *reinterpret_cast<const uint4*>(A + (long long)(m0 + rr) * lda + k0 + kk) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int c = threadIdx.x + 128 * j;
+      const int rr = c / 4, kk = (c % 4) * 8;
+      rb[j] = (n0 + rr < N && k0 + kk < K) ? *reinterpret_cast<const uint4*>(B + (long long)(n0 + rr) * ldb + k0 + kk) : make_uint4(0u, 0u, 0u, 0u);
     }
   };
   fetch(0);
   for (int k0 = 0; k0 < K; k0 += BK) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int i = threadIdx.x + 128 * j;
-      const int rr = i / (BK / 2), kk = (i % (BK / 2)) * 2;
-      *reinterpret_cast<unsigned*>(&As[rr][kk]) = ra[j];
-      *reinterpret_cast<unsigned*>(&Bs[rr][kk]) = rb[j];
+    for (int j = 0; j < ACH; ++j) {
+      const int c = threadIdx.x + 128 * j;
+      if constexpr (sizeof(TA) == 2) {
+        *reinterpret_cast<uint4*>(&As[c / 4][(c % 4) * 8]) = ra[j];
+      } else {
+        const float4 f = *reinterpret_cast<const float4*>(&ra[j]);
+        *reinterpret_cast<uint2*>(&As[c / 8][(c % 8) * 4]) = make_uint2(pack_bf16(f.x, f.y), pack_bf16(f.z, f.w));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int c = threadIdx.x + 128 * j;
+      *reinterpret_cast<uint4*>(&Bs[c / 4][(c % 4) * 8]) = rb[j];
     }
     __syncthreads();
     if (k0 + BK < K) fetch(k0 + BK);
