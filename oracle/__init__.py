@@ -1,7 +1,7 @@
 """CPU oracle for the Mimi + Moshi-LM streaming hot path.
 
 TEST INFRASTRUCTURE ONLY.  Nothing under ``moshi_b200/`` imports this package; it is used by
-``tests/``, by ``__graft_entry__.smoke()`` as the checker, and by ``bench.py`` for the
+``tests/``, by ``__graft_entry__.smoke()`` to compare against, and by ``bench.py`` for the
 ``cpu_baseline`` / ``--impl reference`` timing leg.
 
 The oracle restates, as plain functional PyTorch-on-CPU code with explicit state, the algorithms of
