@@ -193,7 +193,7 @@ int pick_split(int forced, int tiles, int max_ctx, int rpt, int r, size_t part_f
   const int key_tiles = ceil_div(max_ctx, 32);
   int nsplit = 1;
   if (forced > 0) nsplit = std::min(forced, 64);
-  else if (tiles < 148) nsplit = std::min(std::max(296 / tiles, 1), 64);      // one wave of two CTAs per SM
+  else if (tiles < 148) nsplit = std::min(std::max(444 / tiles, 1), 64);      // one wave of three CTAs per SM
   nsplit = std::max(1, std::min(nsplit, key_tiles));
   nsplit = ceil_div(key_tiles, ceil_div(key_tiles, nsplit));                   // no split without a key tile
   while (nsplit > 1 && (size_t)tiles * nsplit * rpt * (r + 2) > part_floats) --nsplit;
@@ -202,7 +202,7 @@ int pick_split(int forced, int tiles, int max_ctx, int rpt, int r, size_t part_f
 
 template <int NKS>
 int launch_attn_mma(cudaStream_t st, const AttnParams& p, int tiles) {
-  const size_t smem = (size_t)2 * 32 * (p.r + 8) * 2 + (size_t)4 * 16 * 36 * 4;
+  const size_t smem = (size_t)2 * 32 * (p.r + 8) * 2 + (size_t)4 * 16 * 32 * 4;
   static bool attr_set = false;
   if (!attr_set) {
     B200_CUDA(cudaFuncSetAttribute(latent_attn_mma_kernel<NKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));

@@ -391,8 +391,10 @@ __device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* 
 }
 
 template <int NKS>      // 16-element steps of a warp's share of the latent: r = 64 * NKS
-__global__ void __launch_bounds__(128) latent_attn_mma_kernel(AttnParams p) {
-  constexpr int KT = 32, R = 64 * NKS, SL = 16 * NKS, STRIDE = R + 8, SPS = 36;     // r = 512: 74 KB per CTA, three CTAs per SM
+__global__ void __launch_bounds__(128, 3) latent_attn_mma_kernel(AttnParams p) {
+  // r = 512: 73 KB per CTA, three CTAs per SM.  A row of partial scores is 32 floats; its 8-float blocks are permuted by the
+  // row (block ^ (row & 3)) so that neither the stores nor the loads of a half-warp meet in a bank.
+  constexpr int KT = 32, R = 64 * NKS, SL = 16 * NKS, STRIDE = R + 8, SPS = 32;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* cs = reinterpret_cast<bf16*>(smem_raw);                                     // [2][KT][STRIDE]
   float* sp = reinterpret_cast<float*>(smem_raw + (size_t)2 * KT * STRIDE * 2);     // [4 warps][16][SPS] partial scores
@@ -474,8 +476,9 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(AttnParams p) {
     float* mine = sp + warp * 16 * SPS;
 #pragma unroll
     for (int nb = 0; nb < 4; ++nb) {
-      *reinterpret_cast<float2*>(mine + g * SPS + nb * 8 + 2 * t4) = make_float2(sacc[nb][0], sacc[nb][1]);
-      *reinterpret_cast<float2*>(mine + (g + 8) * SPS + nb * 8 + 2 * t4) = make_float2(sacc[nb][2], sacc[nb][3]);
+      const int col = ((nb ^ (g & 3)) << 3) + 2 * t4;
+      *reinterpret_cast<float2*>(mine + g * SPS + col) = make_float2(sacc[nb][0], sacc[nb][1]);
+      *reinterpret_cast<float2*>(mine + (g + 8) * SPS + col) = make_float2(sacc[nb][2], sacc[nb][3]);
     }
     __syncthreads();
     // softmax update of rows g, g + 8 on the summed scores; this thread holds keys {2t, 2t+1} + 8 * q, q = 0..3
@@ -491,11 +494,11 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(AttnParams p) {
         float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-          const float2 v = *reinterpret_cast<const float2*>(sp + (w * 16 + lr) * SPS + q * 8 + 2 * t4);
+          const float2 v = *reinterpret_cast<const float2*>(sp + (w * 16 + lr) * SPS + ((q ^ (g & 3)) << 3) + 2 * t4);
           acc.x += v.x; acc.y += v.y;
         }
         const int key = j0 + q * 8 + 2 * t4;
-        s[2 * q] = key <= pos[hf] ? acc.x : -INFINITY;
+        s[2 * q] = key <= pos[hf] ? acc.x : -INFINITY;             // also hides the zero-filled keys past the last one
         s[2 * q + 1] = key + 1 <= pos[hf] ? acc.y : -INFINITY;
       }
       float mx = s[0];
@@ -515,8 +518,10 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(AttnParams p) {
       pf[0][hf] = pack_bf16(s[0], s[1]); pf[0][2 + hf] = pack_bf16(s[2], s[3]);
       pf[1][hf] = pack_bf16(s[4], s[5]); pf[1][2 + hf] = pack_bf16(s[6], s[7]);
     }
+    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {      // a running maximum moved somewhere in the warp
 #pragma unroll
-    for (int i = 0; i < 2 * NKS; ++i) { oacc[i][0] *= corr[0]; oacc[i][1] *= corr[0]; oacc[i][2] *= corr[1]; oacc[i][3] *= corr[1]; }
+      for (int i = 0; i < 2 * NKS; ++i) { oacc[i][0] *= corr[0]; oacc[i][1] *= corr[0]; oacc[i][2] *= corr[1]; oacc[i][3] *= corr[1]; }
+    }
     // weighted sum over this warp's output columns
 #pragma unroll
     for (int k2 = 0; k2 < 2; ++k2) {

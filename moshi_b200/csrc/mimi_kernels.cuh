@@ -8,7 +8,7 @@
 //     transformer.py:972-981, is folded into the neighbouring conv's addressing).
 //   * conv weights are repacked once at load: Conv1d  [Cout][Cin][K] -> [Cout][K*Cin] (tap-major,
 //     channel fastest) so a K-chunk of the implicit GEMM shares one tap.
-// Since round 2 only the learnt down-sampling conv (replicate padding) still runs on igemm_f32_kernel; every other
+// Only the learnt down-sampling conv (replicate padding) still runs on igemm_f32_kernel; every other
 // contraction of the codec is on the tensor cores (mimi_tc.cuh).
 #pragma once
 
