@@ -202,7 +202,7 @@ int pick_split(int forced, int tiles, int max_ctx, int rpt, int r, size_t part_f
 
 template <int NKS>
 int launch_attn_mma(cudaStream_t st, const AttnParams& p, int tiles) {
-  const size_t smem = (size_t)2 * 32 * (p.r + 8) * 2 + (size_t)4 * 16 * 32 * 4;
+  const size_t smem = (size_t)2 * 32 * (p.r + 8) * 2 + (size_t)4 * 16 * 32 * 4 + (size_t)16 * 40 * 2 + (size_t)3 * 16 * 4;      // keys, partial scores, weights, row state
   static bool attr_set = false;
   if (!attr_set) {
     B200_CUDA(cudaFuncSetAttribute(latent_attn_mma_kernel<NKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));

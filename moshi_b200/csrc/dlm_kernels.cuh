@@ -392,12 +392,14 @@ __device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* 
 
 template <int NKS>      // 16-element steps of a warp's share of the latent: r = 64 * NKS
 __global__ void __launch_bounds__(128, 3) latent_attn_mma_kernel(AttnParams p) {
-  // r = 512: 73 KB per CTA, three CTAs per SM.  A row of partial scores is 32 floats; its 8-float blocks are permuted by the
-  // row (block ^ (row & 3)) so that neither the stores nor the loads of a half-warp meet in a bank.
-  constexpr int KT = 32, R = 64 * NKS, SL = 16 * NKS, STRIDE = R + 8, SPS = 32;
+  // r = 512: 75 KB per CTA, three CTAs per SM.  A row of partial scores is 32 floats; its 8-float blocks are permuted by the
+  // row (block ^ (row & 3)) so that neither the stores nor the loads meet in a bank.
+  constexpr int KT = 32, R = 64 * NKS, SL = 16 * NKS, STRIDE = R + 8, SPS = 32, PST = 40;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* cs = reinterpret_cast<bf16*>(smem_raw);                                     // [2][KT][STRIDE]
+  bf16* cs = reinterpret_cast<bf16*>(smem_raw);                                     // [2][KT][STRIDE] keys
   float* sp = reinterpret_cast<float*>(smem_raw + (size_t)2 * KT * STRIDE * 2);     // [4 warps][16][SPS] partial scores
+  bf16* pb = reinterpret_cast<bf16*>(sp + 4 * 16 * SPS);                            // [16][PST] softmax weights of the tile
+  float* stat = reinterpret_cast<float*>(pb + 16 * PST);                            // [3][16]: rescale factor, maximum, sum
   const int tile = blockIdx.x, split = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
   const int H = p.H;
@@ -409,18 +411,13 @@ __global__ void __launch_bounds__(128, 3) latent_attn_mma_kernel(AttnParams p) {
   const int kt0 = split * per, kt1 = min(n_kt, kt0 + per);
   const int col0 = warp * SL;
 
-  // rows g and g + 8 of the tile
-  int pos[2]; float m[2], l[2];
+  // query fragments of rows g and g + 8, this warp's share of the latent
   unsigned qf[NKS][4];
 #pragma unroll
   for (int hf = 0; hf < 2; ++hf) {
     const int lr = g + 8 * hf;
     const bool valid = lr < nrows;
-    const int gr = row0 + (valid ? lr : 0);
-    pos[hf] = valid ? p.tok_pos[gr / H] : -1;
-    if (valid && split == 0) { m[hf] = p.sink[gr % H]; l[hf] = t4 == 0 ? 1.f : 0.f; }
-    else { m[hf] = valid ? -INFINITY : 0.f; l[hf] = 0.f; }
-    const float* qrow = p.qa + (long long)gr * R + col0;
+    const float* qrow = p.qa + (long long)(row0 + (valid ? lr : 0)) * R + col0;
 #pragma unroll
     for (int ks = 0; ks < NKS; ++ks) {
       const float2 a = valid ? *reinterpret_cast<const float2*>(qrow + ks * 16 + 2 * t4) : make_float2(0.f, 0.f);
@@ -428,6 +425,16 @@ __global__ void __launch_bounds__(128, 3) latent_attn_mma_kernel(AttnParams p) {
       qf[ks][hf] = pack_bf16(a.x, a.y);
       qf[ks][2 + hf] = pack_bf16(b.x, b.y);
     }
+  }
+  // softmax state of one row: warp w owns rows 4w .. 4w + 3, eight lanes per row, lane kq of them keys 4 kq .. 4 kq + 3 of a tile
+  const int orow = 4 * warp + (lane >> 3), kq = lane & 7;
+  int opos; float om, ol;
+  {
+    const bool valid = orow < nrows;
+    const int gr = row0 + (valid ? orow : 0);
+    opos = valid ? p.tok_pos[gr / H] : -1;
+    if (valid && split == 0) { om = p.sink[gr % H]; ol = 1.f; }      // the sink: weight exp(sink) in the denominator, no value
+    else { om = valid ? -INFINITY : 0.f; ol = 0.f; }
   }
   float oacc[2 * NKS][4];
 #pragma unroll
@@ -481,68 +488,65 @@ __global__ void __launch_bounds__(128, 3) latent_attn_mma_kernel(AttnParams p) {
       *reinterpret_cast<float2*>(mine + (g + 8) * SPS + col) = make_float2(sacc[nb][2], sacc[nb][3]);
     }
     __syncthreads();
-    // softmax update of rows g, g + 8 on the summed scores; this thread holds keys {2t, 2t+1} + 8 * q, q = 0..3
-    const int j0 = kt * KT;
-    unsigned pf[2][4];
-    float corr[2];
+    // softmax update of the owned row on the summed scores, once per row; the weights go back as bf16
+    {
+      const int pc = (((kq >> 1) ^ (orow & 3)) << 3) + (kq & 1) * 4;
+      float4 a = *reinterpret_cast<const float4*>(sp + orow * SPS + pc);
 #pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-      float s[8];
-      const int lr = g + 8 * hf;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        float2 acc = make_float2(0.f, 0.f);
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          const float2 v = *reinterpret_cast<const float2*>(sp + (w * 16 + lr) * SPS + ((q ^ (g & 3)) << 3) + 2 * t4);
-          acc.x += v.x; acc.y += v.y;
-        }
-        const int key = j0 + q * 8 + 2 * t4;
-        s[2 * q] = key <= pos[hf] ? acc.x : -INFINITY;             // also hides the zero-filled keys past the last one
-        s[2 * q + 1] = key + 1 <= pos[hf] ? acc.y : -INFINITY;
+      for (int w = 1; w < 4; ++w) {
+        const float4 v = *reinterpret_cast<const float4*>(sp + (w * 16 + orow) * SPS + pc);
+        a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
       }
-      float mx = s[0];
-#pragma unroll
-      for (int i = 1; i < 8; ++i) mx = fmaxf(mx, s[i]);
+      const int key = kt * KT + 4 * kq;                    // the mask also hides the zero-filled keys past the last one
+      float s0 = key <= opos ? a.x : -INFINITY, s1 = key + 1 <= opos ? a.y : -INFINITY;
+      float s2 = key + 2 <= opos ? a.z : -INFINITY, s3 = key + 3 <= opos ? a.w : -INFINITY;
+      float mx = fmaxf(fmaxf(s0, s1), fmaxf(s2, s3));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-      const float mn = fmaxf(m[hf], mx);
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      const float mn = fmaxf(om, mx);
       const float mu = mn == -INFINITY ? 0.f : mn;
-      corr[hf] = __expf(m[hf] - mu);                 // m = -inf -> 0 (nothing accumulated yet)
-      float sum = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) { s[i] = __expf(s[i] - mu); sum += s[i]; }
-      l[hf] = l[hf] * corr[hf] + sum;
-      m[hf] = mn;
-      // A fragments of the weights: k-step 0 = keys 0..15 (q = 0, 1), k-step 1 = keys 16..31 (q = 2, 3)
-      pf[0][hf] = pack_bf16(s[0], s[1]); pf[0][2 + hf] = pack_bf16(s[2], s[3]);
-      pf[1][hf] = pack_bf16(s[4], s[5]); pf[1][2 + hf] = pack_bf16(s[6], s[7]);
+      const float corr = __expf(om - mu);                  // om = -inf -> 0 (nothing accumulated yet)
+      s0 = __expf(s0 - mu); s1 = __expf(s1 - mu); s2 = __expf(s2 - mu); s3 = __expf(s3 - mu);
+      float sum = (s0 + s1) + (s2 + s3);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      ol = ol * corr + sum;
+      om = mn;
+      *reinterpret_cast<uint2*>(pb + orow * PST + 4 * kq) = make_uint2(pack_bf16(s0, s1), pack_bf16(s2, s3));
+      if (kq == 0) stat[orow] = corr;
     }
-    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {      // a running maximum moved somewhere in the warp
+    __syncthreads();
+    const float corr0 = stat[g], corr1 = stat[g + 8];
+    if (__any_sync(0xffffffffu, corr0 != 1.f || corr1 != 1.f)) {      // a running maximum moved somewhere in the warp
 #pragma unroll
-      for (int i = 0; i < 2 * NKS; ++i) { oacc[i][0] *= corr[0]; oacc[i][1] *= corr[0]; oacc[i][2] *= corr[1]; oacc[i][3] *= corr[1]; }
+      for (int i = 0; i < 2 * NKS; ++i) { oacc[i][0] *= corr0; oacc[i][1] *= corr0; oacc[i][2] *= corr1; oacc[i][3] *= corr1; }
     }
-    // weighted sum over this warp's output columns
+    // weighted sum over this warp's output columns; A fragments of the weights: k-step 0 = keys 0..15, k-step 1 = keys 16..31
 #pragma unroll
     for (int k2 = 0; k2 < 2; ++k2) {
+      unsigned pf[4];
+      ldmatrix_x4(pf, pb + ((lane & 7) + 8 * ((lane >> 3) & 1)) * PST + 16 * k2 + 8 * (lane >> 4));
 #pragma unroll
       for (int np = 0; np < NKS; ++np) {
         unsigned b[4];
         const int mi = lane >> 3;
         ldmatrix_x4_trans(b, ct + (k2 * 16 + (mi & 1) * 8 + (lane & 7)) * STRIDE + col0 + np * 16 + (mi >> 1) * 8);
-        mma_bf16_16816(oacc[2 * np], pf[k2], b[0], b[1]);
-        mma_bf16_16816(oacc[2 * np + 1], pf[k2], b[2], b[3]);
+        mma_bf16_16816(oacc[2 * np], pf, b[0], b[1]);
+        mma_bf16_16816(oacc[2 * np + 1], pf, b[2], b[3]);
       }
     }
   }
 
+  __syncthreads();                                        // the last tile's rescale factors have been read
+  if (kq == 0) { stat[16 + orow] = om; stat[32 + orow] = ol; }
+  __syncthreads();
 #pragma unroll
   for (int hf = 0; hf < 2; ++hf) {
     const int lr = g + 8 * hf;
-    float lt = l[hf];
-    lt += __shfl_xor_sync(0xffffffffu, lt, 1);
-    lt += __shfl_xor_sync(0xffffffffu, lt, 2);
     if (lr >= nrows) continue;
+    const float mt = stat[16 + lr], lt = stat[32 + lr];
     if (p.nsplit == 1) {
       const float inv = 1.f / lt;
       float* dst = p.out + (long long)(row0 + lr) * R + col0;
@@ -554,7 +558,7 @@ __global__ void __launch_bounds__(128, 3) latent_attn_mma_kernel(AttnParams p) {
 #pragma unroll
       for (int nb = 0; nb < 2 * NKS; ++nb)
         *reinterpret_cast<float2*>(dst + col0 + nb * 8 + 2 * t4) = make_float2(oacc[nb][2 * hf], oacc[nb][2 * hf + 1]);
-      if (warp == 0 && t4 == 0) { dst[R] = m[hf]; dst[R + 1] = lt; }
+      if (warp == 0 && t4 == 0) { dst[R] = mt; dst[R + 1] = lt; }
     }
   }
 }
