@@ -202,7 +202,7 @@ int pick_split(int forced, int tiles, int max_ctx, int rpt, int r, size_t part_f
 
 template <int NKS>
 int launch_attn_mma(cudaStream_t st, const AttnParams& p, int tiles) {
-  const size_t smem = (size_t)2 * 32 * (p.r + 8) * 2 + (size_t)4 * 16 * 32 * 4 + (size_t)16 * 40 * 2 + (size_t)3 * 16 * 4;      // keys, partial scores, weights, row state
+  const size_t smem = (size_t)2 * 32 * (p.r + 8) * 2 + (size_t)4 * 16 * 32 * 4 + (size_t)16 * 40 * 2 + (size_t)3 * 16 * 4 + 16;      // keys, partial scores, weights, row state, mbarriers
   static bool attr_set = false;
   if (!attr_set) {
     B200_CUDA(cudaFuncSetAttribute(latent_attn_mma_kernel<NKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
@@ -249,7 +249,7 @@ int attention(b200_dlm* h, const Layer& L, int max_ctx) {
   p.qa = h->qa; p.cache = L.cache; p.sink = L.sink;
   p.tile_row0 = h->meta_dev + s.off_row0; p.tile_rows = h->meta_dev + s.off_rows; p.tile_slot = h->meta_dev + s.off_slot;
   p.tok_pos = h->meta_dev + h->off_pos;
-  p.out = h->ol; p.part = h->part; p.cap = h->cap; p.r = L.c.kv_rank; p.H = L.c.heads;
+  p.out = h->ol; p.part = h->part; p.cap = h->cap; p.r = L.c.kv_rank; p.H = L.c.heads; p.err = h->err;
   p.nsplit = pick_split(h->attn_split, s.count, max_ctx, s.rpt, p.r, h->part_floats);
   return run_attention<T>(h->stream, p, s.count, s.rpt, h->attn_tc != 0);
 }

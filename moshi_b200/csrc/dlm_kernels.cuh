@@ -4,13 +4,14 @@
 #pragma once
 
 #include "common.cuh"
+#include "tc_prims.cuh"
 
 namespace b200 {
 namespace dlm {
 
 using bf16 = __nv_bfloat16;
 
-enum { ERR_TOKEN = 1 };      // device error flag: a token id outside the embedding table
+enum { ERR_TOKEN = 1, ERR_WAIT = 2 };      // device error flags: a token id outside the embedding table; a copy into shared memory that never arrived
 
 __device__ __forceinline__ float to_f(float v) { return v; }
 __device__ __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }
@@ -207,6 +208,7 @@ struct AttnParams {
   float* out;               // [rows][r]
   float* part;              // nsplit > 1: [tile][split][rows_per_tile][r + 2]
   int cap, r, H, nsplit;
+  int* err = nullptr;       // device error flags (may be null)
 };
 
 template <typename T, int NCH, int RPW>
@@ -390,9 +392,29 @@ __device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* 
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
+// Waits for a phase of an mbarrier, at most about two seconds (wall clock, sampled every 1024 polls); false when it gave up.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+  uint32_t done, spins = 0;
+  uint64_t t0 = 0;
+  for (;;) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+    if ((++spins & 1023u) == 0u) {
+      const uint64_t now = tcp::global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 2000000000ull) return false;
+    }
+  }
+}
+
 template <int NKS>      // 16-element steps of a warp's share of the latent: r = 64 * NKS
 __global__ void __launch_bounds__(128, 3) latent_attn_mma_kernel(AttnParams p) {
-  // r = 512: 75 KB per CTA, three CTAs per SM.  A row of partial scores is 32 floats; its 8-float blocks are permuted by the
+  // r = 512: 75 KB per CTA, three CTAs per SM.  Keys arrive by bulk copies (one per key, issued by the lanes of warp 0) that
+  // complete on an mbarrier per buffer, so no thread spends instructions on staging.  A row of partial scores is 32 floats; its 8-float blocks are permuted by the
   // row (block ^ (row & 3)) so that neither the stores nor the loads meet in a bank.
   constexpr int KT = 32, R = 64 * NKS, SL = 16 * NKS, STRIDE = R + 8, SPS = 32, PST = 40;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -400,6 +422,7 @@ __global__ void __launch_bounds__(128, 3) latent_attn_mma_kernel(AttnParams p) {
   float* sp = reinterpret_cast<float*>(smem_raw + (size_t)2 * KT * STRIDE * 2);     // [4 warps][16][SPS] partial scores
   bf16* pb = reinterpret_cast<bf16*>(sp + 4 * 16 * SPS);                            // [16][PST] softmax weights of the tile
   float* stat = reinterpret_cast<float*>(pb + 16 * PST);                            // [3][16]: rescale factor, maximum, sum
+  const uint32_t bars = tcp::smem_u32(stat + 48);                                   // [2] mbarriers: keys of a buffer have landed
   const int tile = blockIdx.x, split = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
   const int H = p.H;
@@ -440,30 +463,32 @@ __global__ void __launch_bounds__(128, 3) latent_attn_mma_kernel(AttnParams p) {
 #pragma unroll
   for (int i = 0; i < 2 * NKS; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
 
-  auto stage = [&](int kt, int buf) {
+  // Keys past the request's last one are masked, but their (zero) weights still multiply what the buffer holds: make it finite.
+  if (kt1 == n_kt && kt0 < kt1) {
+    const int nk = kmax + 1 - (n_kt - 1) * KT;
+    bf16* dst = cs + (size_t)((n_kt - 1 - kt0) & 1) * KT * STRIDE + nk * STRIDE;
+    for (int c = threadIdx.x; c < (KT - nk) * STRIDE / 8; c += 128) reinterpret_cast<uint4*>(dst)[c] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  if (threadIdx.x == 0) {
+    tcp::mbar_init(bars, 1);
+    tcp::mbar_init(bars + 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncthreads();
+  auto issue = [&](int kt, int buf) {                       // warp 0: lane j copies key j of the tile
     const int j0 = kt * KT, nk = min(KT, kmax + 1 - j0);
-    constexpr int CPR = R / 8;                                   // 16-byte chunks per key
-    bf16* dst = cs + (size_t)buf * KT * STRIDE;
-    const bf16* src = cbase + (long long)j0 * R;
-    for (int c = threadIdx.x; c < KT * CPR; c += 128) {
-      const int row = c / CPR, cc = c - row * CPR;
-      bf16* d = dst + row * STRIDE + cc * 8;
-      if (row < nk) {
-        const unsigned sa = (unsigned)__cvta_generic_to_shared(d);
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(src + (long long)row * R + cc * 8));
-      } else {
-        *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
-      }
-    }
-    asm volatile("cp.async.commit_group;\n" ::);
+    const uint32_t bar = bars + 8 * buf;
+    if (lane == 0) tcp::mbar_expect_tx(bar, (uint32_t)nk * R * 2);
+    __syncwarp();
+    if (lane < nk) tcp::bulk_load(tcp::smem_u32(cs + ((size_t)buf * KT + lane) * STRIDE), cbase + (long long)(j0 + lane) * R, R * 2, bar);
   };
 
-  if (kt0 < kt1) stage(kt0, 0);
+  if (warp == 0 && kt0 < kt1) issue(kt0, 0);
+  bool arrived = true;
   for (int kt = kt0; kt < kt1; ++kt) {
     const int buf = (kt - kt0) & 1;
-    asm volatile("cp.async.wait_group 0;\n" ::);
-    __syncthreads();
-    if (kt + 1 < kt1) stage(kt + 1, buf ^ 1);
+    if (arrived) arrived = mbar_wait_bounded(bars + 8 * buf, ((kt - kt0) >> 1) & 1);
     const bf16* ct = cs + (size_t)buf * KT * STRIDE;
     // partial scores of this warp's share of the latent: [16 rows][32 keys]
     float sacc[4][4];
@@ -488,6 +513,7 @@ __global__ void __launch_bounds__(128, 3) latent_attn_mma_kernel(AttnParams p) {
       *reinterpret_cast<float2*>(mine + (g + 8) * SPS + col) = make_float2(sacc[nb][2], sacc[nb][3]);
     }
     __syncthreads();
+    if (warp == 0 && kt + 1 < kt1) issue(kt + 1, buf ^ 1);      // every warp is done with the other buffer (tile kt - 1)
     // softmax update of the owned row on the summed scores, once per row; the weights go back as bf16
     {
       const int pc = (((kq >> 1) ^ (orow & 3)) << 3) + (kq & 1) * 4;
@@ -539,7 +565,7 @@ __global__ void __launch_bounds__(128, 3) latent_attn_mma_kernel(AttnParams p) {
     }
   }
 
-  __syncthreads();                                        // the last tile's rescale factors have been read
+  if (!arrived && p.err != nullptr) atomicOr(p.err, ERR_WAIT);
   if (kq == 0) { stat[16 + orow] = om; stat[32 + orow] = ol; }
   __syncthreads();
 #pragma unroll
