@@ -256,6 +256,20 @@ def test_long_decoding_token_by_token():
     assert_close(torch.cat(rows), want[19:], torch.float32)
 
 
+def test_long_decoding_on_the_tensor_core_attention():
+    """bfloat16, latents the tensor-core kernel takes: 100 single tokens cross three 32-key tile edges, the number of key splits
+    changes on the way, and no copy into shared memory is ever given up on (device error flags stay 0)."""
+    model, orc = build(TCATTN, torch.bfloat16)
+    toks = tokens(131, TCATTN.vocab, 8)
+    want = orc.forward(toks)
+    with gen_for(model) as gen:
+        rows = [gen.step([(1, toks[:31])], [30]).cpu()]
+        for t in range(31, 131):
+            rows.append(gen.step([(1, [toks[t]])], [0]).cpu())
+        assert gen.error_flags() == 0
+    assert_close(torch.cat(rows), want[30:], torch.bfloat16)
+
+
 @pytest.mark.parametrize("cfg", [ODD, TCATTN], ids=["odd", "tcattn"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_unequal_batch_equals_each_request_alone(dtype, cfg):
