@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define B200_ABI_VERSION 3
+#define B200_ABI_VERSION 4
 
 enum {
   B200_OK = 0,
@@ -332,28 +332,65 @@ int b200_frame_read_buffer(b200_frame* f, const char* name, void* dst_dev, int64
  *           (keys / values are W_uk c / W_uv c per head), softmax with one learnt sink logit per head in the denominator;
  *           ONLY c is cached, the kernels score against it directly (W_uk folded into the query, W_uv applied after the sum)
  *   mlp     B200_MLP_NONE, B200_MLP_DENSE_RELU2: W_down relu(W_up h)^2
+ * and (the Govuvik design):
+ *   block   B200_BLOCK_SANDWICH: RMS norms before and after every sublayer, x += norm_b(sublayer(norm(x))), mixer then
+ *           feed-forward; the embedding output is RMS-normed; what the mixer reads first gets h + conv(h), a causal per-channel
+ *           convolution over time (canon_taps taps; 0 = none) whose last inputs are carried per request; logits are capped
+ *           by logit_softcap * tanh(. / logit_softcap) (0 = no cap)
+ *   mixer   B200_MIXER_WINDOW_ATTENTION: sliding-window attention with grouped key/value heads, a causal convolution on
+ *           the projected q, k, v (conv_taps), RMS norm over the whole q / k projection, rotary positions on the first
+ *           rot_dims dimensions of a head (half-split pairs; frequencies rescaled by wavelength when rot_factor > 0), per-head
+ *           temperature, scores mixed over heads by an H x H matrix before the softmax, and a sink logit per head
+ *           B200_MIXER_GLA: matrix memory with a decay per key channel, a = sigmoid(W_a2 W_a1 h + b)^(1 / tau); the output is
+ *           RMS-normed per head (one weight row shared by the heads) and gated by silu(W_g h)
+ *           B200_MIXER_MLSTM: matrix memory with exponential input gate and sigmoid forget gate (both capped by
+ *           gate_cap * tanh(. / gate_cap)), a running maximum and a normaliser vector; the output is divided by its
+ *           per-head root mean square, weighted, and gated by sigmoid(W_g h)
+ *           B200_MIXER_PARALLEL: mixers a (tensors "mix.left.*") and b ("mix.right.*") read the same input; the result is
+ *           half the sum of their outputs, each RMS-normed over the width ("mix.left.out", "mix.right.out")
+ *   mlp     B200_MLP_MOE_RELU2: `experts` feed-forwards W_down relu(W_up h)^2 of hidden size ff; a token uses the `top` ones
+ *           with the largest router logits (fp32), weighted by the softmax over those logits alone
  * Precision: compute_dtype B200_BF16 = bf16 weights / activations / cache with fp32 accumulation, while norms, attention
- * scores and weights, gates, the residual stream and the depth average stay fp32; B200_F32 = everything in IEEE fp32 (FMA).
+ * scores and weights, gates, routers, recurrent state, the residual stream and the depth average stay fp32; B200_F32 =
+ * everything in IEEE fp32 (FMA).
  * Requests live in cache SLOTS of `capacity` tokens; a step runs a ragged batch (any number of new tokens per slot) on top
- * of what earlier steps left in the slots.  Logits at a position do not depend on how its request was cut into steps. */
+ * of what earlier steps left in the slots (cached keys / values / latents, carried convolution inputs, recurrent state).
+ * Logits at a position do not depend on how its request was cut into steps. */
 typedef struct b200_dlm b200_dlm;
 
-enum { B200_MIXER_LATENT_ATTENTION = 1 };
-enum { B200_MLP_NONE = 0, B200_MLP_DENSE_RELU2 = 1 };
+enum { B200_MIXER_LATENT_ATTENTION = 1, B200_MIXER_WINDOW_ATTENTION = 2, B200_MIXER_GLA = 3, B200_MIXER_MLSTM = 4, B200_MIXER_PARALLEL = 5 };
+enum { B200_MLP_NONE = 0, B200_MLP_DENSE_RELU2 = 1, B200_MLP_MOE_RELU2 = 2 };
+enum { B200_BLOCK_GATED_DEPTH_AVERAGE = 0, B200_BLOCK_SANDWICH = 1 };
 
 typedef struct {
-  int mixer;                  /* B200_MIXER_*                                                   */
+  int kind;                   /* B200_MIXER_* (not PARALLEL)                                    */
   int heads, dim, vdim;       /* per head: query/key size, value size                           */
-  int kv_rank;                /* size of the cached latent                                      */
+  int kv_heads;               /* window attention: key/value heads (query head h uses h / (heads / kv_heads)) */
+  int kv_rank;                /* latent attention: size of the cached latent                    */
   float scale;                /* multiplies q.k                                                 */
+  int window;                 /* window attention: a token sees itself and window - 1 before it */
+  int conv_taps;              /* window attention: taps of the convolution on q, k, v (<= 1: none) */
+  int rot_dims;               /* rotated dimensions per head (even, <= dim)                     */
+  float rot_base, rot_factor, rot_low, rot_high, rot_original;   /* rot_factor <= 0: frequencies as they are */
+  float gate_cap;             /* mLSTM: cap of both gate pre-activations                        */
+  float tau;                  /* GLA: decay = sigmoid(z)^(1 / tau)                              */
+} b200_dlm_mixer;
+
+typedef struct {
+  int mixer;                  /* B200_MIXER_*; PARALLEL: a and b side by side, else a alone     */
+  b200_dlm_mixer a, b;
   int mlp;                    /* B200_MLP_*                                                     */
-  int ff;                     /* hidden size of the feed-forward                                */
+  int ff;                     /* hidden size of the feed-forward (of one expert)                */
+  int experts, top;           /* routed experts and how many of them a token uses               */
 } b200_dlm_layer;
 
 typedef struct {
   int vocab, width, n_layers;
   float embedding_scale, residual_mult, norm_eps;
   int compute_dtype;          /* B200_BF16 or B200_F32                                          */
+  int block;                  /* B200_BLOCK_*                                                   */
+  int canon_taps;             /* sandwich block: taps of the convolution on the mixer's input   */
+  float logit_softcap;
   const b200_dlm_layer* layers;
 } b200_dlm_config;
 
@@ -372,9 +409,10 @@ int b200_dlm_set_stream(b200_dlm* h, void* stream);
  * cores also where the tensor-core kernel would take it), "time_kernels" (CUDA events around every
  * operation, summed per class: a step then waits for its own end). */
 int b200_dlm_set_option(b200_dlm* h, const char* name, int value);
-/* Milliseconds spent so far per class of operation under "time_kernels": [0] linears, [1] latent attention, [2] the per-head
- * folds around it (query through W_uk, sum through W_uv), [3] element-wise and norm kernels. */
-int b200_dlm_read_timers(b200_dlm* h, double* ms4_host, int reset);
+/* Milliseconds spent so far per class of operation under "time_kernels": [0] linears, [1] attention, [2] the small products
+ * around a mixer (query through W_uk, sum through W_uv; gate and decay projections), [3] element-wise, norm and convolution
+ * kernels, [4] recurrent matrix memories, [5] routed experts (router, grouping, grouped products). */
+int b200_dlm_read_timers(b200_dlm* h, double* ms6_host, int reset);
 /* Gives a slot back: its length becomes 0 (the next request that gets the slot starts at position 0). */
 int b200_dlm_release(b200_dlm* h, int slot);
 int b200_dlm_slot_length(b200_dlm* h, int slot);

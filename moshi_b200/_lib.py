@@ -14,7 +14,7 @@ LIB_PATH = Path(__file__).resolve().parent / "_C" / "libmoshi_b200.so"
 
 B200_OK, B200_ERR_INVALID, B200_ERR_SHAPE, B200_ERR_STATE, B200_ERR_CUDA, B200_ERR_MISSING = range(6)
 B200_F32, B200_BF16, B200_F16, B200_I64, B200_U8, B200_I8 = range(6)
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 
 class MimiConfigC(C.Structure):
@@ -41,14 +41,21 @@ class LMConfigC(C.Structure):
     ]
 
 
+class DLMMixerC(C.Structure):
+    _fields_ = [("kind", C.c_int), ("heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int), ("kv_heads", C.c_int), ("kv_rank", C.c_int),
+                ("scale", C.c_float), ("window", C.c_int), ("conv_taps", C.c_int), ("rot_dims", C.c_int), ("rot_base", C.c_float),
+                ("rot_factor", C.c_float), ("rot_low", C.c_float), ("rot_high", C.c_float), ("rot_original", C.c_float),
+                ("gate_cap", C.c_float), ("tau", C.c_float)]
+
+
 class DLMLayerC(C.Structure):
-    _fields_ = [("mixer", C.c_int), ("heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int), ("kv_rank", C.c_int),
-                ("scale", C.c_float), ("mlp", C.c_int), ("ff", C.c_int)]
+    _fields_ = [("mixer", C.c_int), ("a", DLMMixerC), ("b", DLMMixerC), ("mlp", C.c_int), ("ff", C.c_int), ("experts", C.c_int), ("top", C.c_int)]
 
 
 class DLMConfigC(C.Structure):
     _fields_ = [("vocab", C.c_int), ("width", C.c_int), ("n_layers", C.c_int), ("embedding_scale", C.c_float),
-                ("residual_mult", C.c_float), ("norm_eps", C.c_float), ("compute_dtype", C.c_int), ("layers", C.POINTER(DLMLayerC))]
+                ("residual_mult", C.c_float), ("norm_eps", C.c_float), ("compute_dtype", C.c_int), ("block", C.c_int),
+                ("canon_taps", C.c_int), ("logit_softcap", C.c_float), ("layers", C.POINTER(DLMLayerC))]
 
 
 _P = C.c_void_p

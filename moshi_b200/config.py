@@ -269,21 +269,68 @@ def tiny_lm_config(**over) -> LMConfig:
 # ---------------------------------------------------------------------------------------------------
 # Decoder LMs given as a list of layers (text-only; no reference counterpart)
 # ---------------------------------------------------------------------------------------------------
-MIXERS = {"latent_attention": 1}            # name in config.json -> B200_MIXER_*
-MLP_KINDS = {None: 0, "dense": 1}           # "mlp.kind" (or a null "mlp") -> B200_MLP_*
+MIXERS = {"latent_attention": 1, "window_attention": 2, "gla": 3, "mlstm": 4, "parallel": 5}    # name -> B200_MIXER_*
+MLP_KINDS = {None: 0, "dense": 1, "moe": 2}                                                      # "mlp.kind" (or a null "mlp") -> B200_MLP_*
+BLOCKS = {"gated_depth_average": 0, "sandwich": 1}                                                # block arrangement -> B200_BLOCK_*
+
+
+@dataclass
+class MixerConfig:
+    """One token mixer with its sizes and constants (the fields a kind does not use stay 0).
+
+    ``window_attention``: ``kv_heads`` key/value heads, a token sees itself and the ``window - 1`` tokens before it, a causal
+    convolution of ``conv`` taps on the projected q / k / v, rotary positions on the first ``rot_dims`` dimensions of a head with
+    base ``rot_base`` and (optionally) wavelength-dependent rescaling ``rot_scaling`` = {factor, low, high, original}.
+    ``gla``: per-channel decay sigmoid(z)^(1 / tau), z through a bottleneck of ``decay_rank`` (a tensor's shape, not a config key).
+    ``mlstm``: both gate pre-activations are capped by ``gate_cap * tanh(. / gate_cap)``."""
+    kind: str
+    heads: int
+    dim: int
+    vdim: int
+    kv_heads: int = 0
+    kv_rank: int = 0
+    scale: float = 0.0
+    window: int = 0
+    conv: int = 0
+    rot_dims: int = 0
+    rot_base: float = 10000.0
+    rot_scaling: tp.Optional[dict] = None
+    gate_cap: float = 0.0
+    tau: float = 1.0
+    decay_rank: int = 16
+
+
+def _window_attention_from_dict(m: dict) -> MixerConfig:
+    rot = m.get("rot") or {}
+    return MixerConfig(kind="window_attention", heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                       scale=float(m["scale"]), window=int(m["mask"]["size"]), conv=int(m.get("conv", 0)), rot_dims=int(rot.get("dims", 0)),
+                       rot_base=float(rot.get("base", 10000.0)), rot_scaling=dict(rot["scaling"]) if rot.get("scaling") else None)
+
+
+def _window_attention_to_dict(m: MixerConfig) -> dict:
+    rot: dict = {"base": m.rot_base, "dims": m.rot_dims}
+    if m.rot_scaling:
+        rot["scaling"] = dict(m.rot_scaling)
+    return {"conv": m.conv, "dim": m.dim, "heads": m.heads, "kv_heads": m.kv_heads, "mask": {"size": m.window}, "rot": rot, "scale": m.scale, "vdim": m.vdim}
 
 
 @dataclass
 class DecoderLayerConfig:
-    """One entry of ``layers``: the token mixer with its sizes, and the feed-forward (``mlp_kind`` None = the layer has none)."""
+    """One entry of ``layers``: the token mixer with its sizes, and the feed-forward (``mlp_kind`` None = the layer has none).
+    The flat fields describe a ``latent_attention`` mixer; the other kinds are carried as ``MixerConfig`` in ``a`` (the only
+    mixer, or the left one of a ``parallel`` pair) and ``b`` (the right one)."""
     type: str
-    heads: int
-    dim: int
-    vdim: int
-    kv_rank: int
-    scale: float
+    heads: int = 0
+    dim: int = 0
+    vdim: int = 0
+    kv_rank: int = 0
+    scale: float = 0.0
     mlp_kind: tp.Optional[str] = "dense"
     ff: int = 0
+    a: tp.Optional[MixerConfig] = None
+    b: tp.Optional[MixerConfig] = None
+    experts: int = 0
+    top: int = 0
 
     @staticmethod
     def from_dict(d: dict) -> "DecoderLayerConfig":
@@ -294,14 +341,46 @@ class DecoderLayerConfig:
         mlp = d.get("mlp")
         if mlp is not None and mlp.get("kind") not in MLP_KINDS:
             raise ValueError(f"unknown feed-forward kind {mlp.get('kind')!r}")
-        return DecoderLayerConfig(type=kind, heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]), kv_rank=int(m["kv_rank"]),
-                                  scale=float(m["scale"]), mlp_kind=None if mlp is None else mlp["kind"],
-                                  ff=0 if mlp is None else int(mlp["ff"]))
+        mlp_kind = None if mlp is None else mlp["kind"]
+        if mlp_kind == "moe":
+            ff, experts, top = int(mlp["expert"]["ff"]), int(mlp["router"]["experts"]), int(mlp["router"]["top"])
+        else:
+            ff, experts, top = (0 if mlp is None else int(mlp["ff"])), 0, 0
+        if kind == "latent_attention":
+            return DecoderLayerConfig(type=kind, heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]), kv_rank=int(m["kv_rank"]),
+                                      scale=float(m["scale"]), mlp_kind=mlp_kind, ff=ff)
+        if kind == "parallel":
+            r = m["right"]
+            a = _window_attention_from_dict(m["left"])
+            b = MixerConfig(kind="gla", heads=int(r["heads"]), dim=int(r["dim"]), vdim=int(r["vdim"]), tau=float(r["tau"]),
+                            decay_rank=int(r.get("decay_rank", 16)))
+        elif kind == "mlstm":
+            a, b = MixerConfig(kind="mlstm", heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]), gate_cap=float(m["gate_cap"])), None
+        else:
+            raise ValueError(f"mixer {kind!r} stands only inside a parallel pair")
+        return DecoderLayerConfig(type=kind, mlp_kind=mlp_kind, ff=ff, a=a, b=b, experts=experts, top=top)
 
     def to_dict(self) -> dict:
-        return {"type": self.type,
-                "mixer": {"heads": self.heads, "dim": self.dim, "vdim": self.vdim, "kv_rank": self.kv_rank, "scale": self.scale},
-                "mlp": None if self.mlp_kind is None else {"kind": self.mlp_kind, "ff": self.ff}}
+        if self.mlp_kind is None:
+            mlp = None
+        elif self.mlp_kind == "moe":
+            mlp = {"expert": {"ff": self.ff}, "kind": "moe", "router": {"experts": self.experts, "top": self.top}}
+        else:
+            mlp = {"kind": self.mlp_kind, "ff": self.ff}
+        if self.type == "parallel":
+            mixer = {"left": _window_attention_to_dict(self.a),
+                     "right": {"dim": self.b.dim, "heads": self.b.heads, "tau": self.b.tau, "vdim": self.b.vdim}}
+        elif self.type == "mlstm":
+            mixer = {"dim": self.a.dim, "gate_cap": self.a.gate_cap, "heads": self.a.heads, "vdim": self.a.vdim}
+        else:
+            mixer = {"heads": self.heads, "dim": self.dim, "vdim": self.vdim, "kv_rank": self.kv_rank, "scale": self.scale}
+        return {"type": self.type, "mixer": mixer, "mlp": mlp}
+
+    def mixers(self) -> tuple:
+        """(a, b) as ``MixerConfig`` whatever the kind (a latent attention's flat fields are wrapped)."""
+        if self.type == "latent_attention":
+            return MixerConfig(kind=self.type, heads=self.heads, dim=self.dim, vdim=self.vdim, kv_rank=self.kv_rank, scale=self.scale), None
+        return self.a, self.b
 
 
 @dataclass
@@ -316,12 +395,17 @@ class DecoderLMConfig:
     embedding_scale: float = 1.0
     residual_mult: float = 1.0
     norm_eps: float = 1e-6
+    block: str = "gated_depth_average"
+    canon_taps: int = 0
+    logit_softcap: float = 0.0
 
     @staticmethod
     def from_dict(d: dict) -> "DecoderLMConfig":
         arch = d.get("architecture")
         if arch not in DECODER_ARCHITECTURES:
             raise ValueError(f"unknown architecture {arch!r} (known: {sorted(DECODER_ARCHITECTURES)})")
+        if DECODER_ARCHITECTURES[arch] is not DecoderLMConfig:
+            return DECODER_ARCHITECTURES[arch].from_dict(d)
         return DecoderLMConfig(architecture=arch, vocab=int(d["vocab"]), width=int(d["width"]),
                                layers=[DecoderLayerConfig.from_dict(x) for x in d["layers"]],
                                embedding_scale=float(d["embedding"]["scale"]), residual_mult=float(d["residual_mult"]),
@@ -353,5 +437,57 @@ class DecoderLMConfig:
         return out
 
 
+@dataclass
+class GovuvikConfig(DecoderLMConfig):
+    """``config.json`` of the Govuvik design: RMS norms before and after every sublayer (mixer, then a routed mixture of
+    experts), an RMS-normed embedding, a causal convolution (``canon.taps``) on what every mixer reads, capped logits.  Layers
+    are ``mlstm`` (a gated matrix memory) or ``parallel`` (sliding-window attention beside gated linear attention)."""
+
+    @staticmethod
+    def from_dict(d: dict) -> "GovuvikConfig":
+        layers = [DecoderLayerConfig.from_dict(x) for x in d["layers"]]
+        for i, L in enumerate(layers):
+            if L.type not in ("parallel", "mlstm") or L.mlp_kind not in (None, "moe"):
+                raise ValueError(f"layer {i}: a Govuvik layer is 'parallel' or 'mlstm' with a 'moe' feed-forward or none")
+        return GovuvikConfig(architecture=d["architecture"], vocab=int(d["vocab"]), width=int(d["width"]), layers=layers,
+                             norm_eps=float(d["norm"]["eps"]), block="sandwich", canon_taps=int((d.get("canon") or {}).get("taps", 0)),
+                             logit_softcap=float(d.get("logit_softcap", 0.0)))
+
+    def to_dict(self) -> dict:
+        return {"architecture": self.architecture, "canon": {"taps": self.canon_taps}, "layers": [x.to_dict() for x in self.layers],
+                "logit_softcap": self.logit_softcap, "norm": {"eps": self.norm_eps}, "vocab": self.vocab, "width": self.width}
+
+    def tensor_shapes(self) -> dict:
+        W = self.width
+        out = {"embed": (self.vocab, W), "embed.norm": (W,)}
+        for i, L in enumerate(self.layers):
+            p = f"l{i}."
+            out.update({p + "norm1": (W,), p + "norm1b": (W,)})
+            if self.canon_taps > 0:
+                out[p + "canon1"] = (W, self.canon_taps)
+            if L.type == "parallel":
+                a, b, l, r = L.a, L.b, p + "mix.left.", p + "mix.right."
+                nq, nk, nv = a.heads * a.dim, a.kv_heads * a.dim, a.kv_heads * a.vdim
+                out.update({l + "q": (nq, W), l + "k": (nk, W), l + "v": (nv, W), l + "q.norm": (nq,), l + "k.norm": (nk,)})
+                if a.conv > 1:
+                    out.update({l + "q.conv": (nq, a.conv), l + "k.conv": (nk, a.conv), l + "v.conv": (nv, a.conv)})
+                out.update({l + "talk": (a.heads, a.heads), l + "temp": (a.heads,), l + "sink": (a.heads,), l + "o": (W, a.heads * a.vdim),
+                            r + "q": (b.heads * b.dim, W), r + "k": (b.heads * b.dim, W), r + "v": (b.heads * b.vdim, W),
+                            r + "g": (b.heads * b.vdim, W), r + "o": (W, b.heads * b.vdim), r + "norm": (b.vdim,),
+                            r + "a1": (b.decay_rank, W), r + "a2": (b.heads * b.dim, b.decay_rank), r + "a2.b": (b.heads * b.dim,),
+                            l + "out": (W,), r + "out": (W,)})
+            else:
+                a, m = L.a, p + "mix."
+                out.update({m + "q": (a.heads * a.dim, W), m + "k": (a.heads * a.dim, W), m + "v": (a.heads * a.vdim, W),
+                            m + "g": (a.heads * a.vdim, W), m + "o": (W, a.heads * a.vdim), m + "norm": (a.heads * a.vdim,),
+                            m + "i": (a.heads, W), m + "i.b": (a.heads,), m + "f": (a.heads, W), m + "f.b": (a.heads,)})
+            if L.mlp_kind == "moe":
+                out.update({p + "norm2": (W,), p + "norm2b": (W,), p + "mlp.router": (L.experts, W)})
+                for e in range(L.experts):
+                    out.update({p + f"mlp.e{e}.up": (L.ff, W), p + f"mlp.e{e}.down": (W, L.ff)})
+        out.update({"final.norm": (W,), "head": (self.vocab, W)})
+        return out
+
+
 # architecture name in config.json -> configuration class (the model registry of the text-only decoder LMs)
-DECODER_ARCHITECTURES: dict = {"Likosun": DecoderLMConfig}
+DECODER_ARCHITECTURES: dict = {"Likosun": DecoderLMConfig, "Govuvik": GovuvikConfig}

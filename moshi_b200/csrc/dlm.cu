@@ -1,9 +1,14 @@
 // Decoder-LM handle: a language model given as a list of layers (mixer + feed-forward per layer), its weights under the
-// checkpoint's names, a slot cache of per-layer latents, and the ragged step (any number of new tokens per slot) that both
-// prompt portions and single-token decoding go through.  The Likosun design is the first user of the registered mechanisms.
+// checkpoint's names, a slot cache per layer (latents, or keys and values, plus the carried inputs of convolutions and the
+// state of recurrent mixers), and the ragged step (any number of new tokens per slot) that both prompt portions and
+// single-token decoding go through.  Two block arrangements are registered: gated parallel sublayers with a depth-weighted
+// average (the Likosun design) and RMS-norm sandwiches around mixer and feed-forward in turn (the Govuvik design).
 #include <algorithm>
 
+#include <cmath>
+
 #include "dlm_kernels.cuh"
+#include "dlm_mixers.cuh"
 #include "gemm_sk.cuh"
 #include "lm_kernels.cuh"
 
@@ -27,6 +32,23 @@ struct Layer {
   float *n1w = nullptr, *n1b = nullptr, *cnorm = nullptr, *sink = nullptr, *b1 = nullptr, *b2 = nullptr, *avg = nullptr;
   void* cache = nullptr;               // [slots][cap][r]
   int sig = 0;                         // index of the layer's attention tile list
+  // ---- sandwich block (norms around every sublayer); a = the only mixer or the left one, b = the right one of a parallel pair
+  float *n2w = nullptr, *n1bw = nullptr, *n2bw = nullptr, *canon = nullptr, *canon_hist = nullptr;
+  // window attention (a)
+  int a_q = 0, a_k = 0, a_v = 0, a_g = 0;         // offsets into the concatenated projection
+  int Nq = 0, Nk = 0, Nv = 0, QT = 0, KT = 0, kstride = 0; size_t attn_smem = 0;
+  float *qnorm = nullptr, *knorm = nullptr, *qkv_conv = nullptr, *qkv_hist = nullptr, *mixhh = nullptr; double* freq = nullptr;
+  void *kcache = nullptr, *vcache = nullptr;
+  Weight a_o;
+  float *a_out = nullptr, *b_out = nullptr;       // norms of the two outputs of a parallel pair
+  // recurrent mixers: GLA (b of a parallel pair) and mLSTM (a)
+  int r_q = 0, r_k = 0, r_v = 0, r_g = 0, r_a1 = 0, decay_rank = 0;
+  void *a2 = nullptr, *w_if = nullptr;            // T [heads * dim][decay_rank];  T [2 * heads][width]
+  float *a2b = nullptr, *if_b = nullptr, *rnorm = nullptr;
+  float *St = nullptr, *nvec = nullptr, *mval = nullptr;
+  Weight r_o;
+  // routed experts
+  void *router = nullptr, *ups = nullptr, *downs = nullptr;      // T [E][width]; T [E][ff][width]; T [E][width][ff]
 };
 
 // attention tile list of one (heads, rows per tile) combination
@@ -49,7 +71,7 @@ struct b200_dlm {
   // option "time_kernels": CUDA events around every operation of a step, summed per class (bench.py's per-kernel roofline)
   int time_kernels = 0;
   std::vector<cudaEvent_t> ev_pool; std::vector<int> ev_class; size_t ev_used = 0;
-  double class_ms[4] = {0, 0, 0, 0};
+  double class_ms[6] = {0, 0, 0, 0, 0, 0};
   void *embed = nullptr;
   Weight head;
   float *fnw = nullptr, *fnb = nullptr;
@@ -68,6 +90,12 @@ struct b200_dlm {
   size_t part_floats = 0;
   int last_tokens = 0, last_want = 0;
   int* err = nullptr;
+  // sandwich block: step metadata per token (first / last token of its request in the step) and per entry, further buffers
+  int off_first = 0, off_last = 0, off_ent_tok0 = 0, off_ent_ntok = 0, off_ent_slot = 0, off_ent_pos0 = 0, n_entries = 0;
+  float *embw = nullptr, *h32 = nullptr, *qkv32 = nullptr, *scan32 = nullptr, *gate32 = nullptr, *attn32 = nullptr, *route32 = nullptr, *moe_w = nullptr;
+  void *mixo2 = nullptr, *obuf2 = nullptr, *yexp = nullptr;
+  int *moe_idx = nullptr, *moe_rank = nullptr, *moe_perm = nullptr, *moe_row_tok = nullptr, *moe_tile_e = nullptr, *moe_tile_r0 = nullptr,
+      *moe_tile_n = nullptr, *moe_ntiles = nullptr;
   float* sk_ws = nullptr; int* sk_counters = nullptr;
   tc::GemmPlanCache plans;
 };
@@ -116,10 +144,10 @@ int put_matrix(b200_dlm* h, const std::string& name, int64_t rows, int64_t K, vo
 }
 
 // bf16 mode + eligible shape: the row-major matrix is replaced by the tcgen05 GEMM's packed tiles
-int seal_weight(b200_dlm* h, Weight& w, void* rm, int N, int K, std::vector<void*>& drop) {
+int seal_weight(b200_dlm* h, Weight& w, void* rm, int N, int K, std::vector<void*>& drop, int ld_out = 0) {
   w.rm = rm; w.N = N; w.K = K; w.tiles = nullptr;
   h->weight_bytes += (int64_t)N * K * esize(h);
-  if (!h->f32 && h->use_tc && K >= 8 && K % 8 == 0 && (N + 127) / 128 <= tc::SK_MAX_TILES) {
+  if (!h->f32 && h->use_tc && K >= 8 && K % 8 == 0 && ld_out % 8 == 0 && (N + 127) / 128 <= tc::SK_MAX_TILES) {
     B200_TRY(h->weights.alloc(&w.tiles, tc::sk_packed_bytes(N, K, 0, 0), false));
     B200_TRY(tc::sk_pack_weights(static_cast<const bf16*>(rm), w.tiles, N, K, 0, 0, nullptr));
     drop.push_back(rm);
@@ -249,12 +277,12 @@ int attention(b200_dlm* h, const Layer& L, int max_ctx) {
   p.qa = h->qa; p.cache = L.cache; p.sink = L.sink;
   p.tile_row0 = h->meta_dev + s.off_row0; p.tile_rows = h->meta_dev + s.off_rows; p.tile_slot = h->meta_dev + s.off_slot;
   p.tok_pos = h->meta_dev + h->off_pos;
-  p.out = h->ol; p.part = h->part; p.cap = h->cap; p.r = L.c.kv_rank; p.H = L.c.heads; p.err = h->err;
+  p.out = h->ol; p.part = h->part; p.cap = h->cap; p.r = L.c.a.kv_rank; p.H = L.c.a.heads; p.err = h->err;
   p.nsplit = pick_split(h->attn_split, s.count, max_ctx, s.rpt, p.r, h->part_floats);
   return run_attention<T>(h->stream, p, s.count, s.rpt, h->attn_tc != 0);
 }
 
-enum { CLS_LINEAR = 0, CLS_ATTN = 1, CLS_FOLD = 2, CLS_ELEMENTWISE = 3 };
+enum { CLS_LINEAR = 0, CLS_ATTN = 1, CLS_FOLD = 2, CLS_ELEMENTWISE = 3, CLS_RECURRENT = 4, CLS_EXPERTS = 5 };
 
 int mark(b200_dlm* h, int cls) {       // cls >= 0 opens an interval of that class, -1 closes the open one
   if (!h->time_kernels) return B200_OK;
@@ -282,7 +310,7 @@ int step_body(b200_dlm* h, int n_tok, int n_want, int max_ctx, float* logits_out
   TIMED(CLS_ELEMENTWISE, B200_LAUNCH(layernorm_kernel<T>, n_tok, 256, 0, st, h->xin, (const int*)nullptr, h->layers[0].n1w, h->layers[0].n1b, hb, W, c.norm_eps));
   for (int li = 0; li < c.n_layers; ++li) {
     const Layer& L = h->layers[li];
-    const int H = L.c.heads, dk = L.c.dim, dv = L.c.vdim, r = L.c.kv_rank;
+    const int H = L.c.a.heads, dk = L.c.a.dim, dv = L.c.a.vdim, r = L.c.a.kv_rank;
     T* proj = static_cast<T*>(h->proj);
     TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, hb, W, L.cat, proj, L.ldp, n_tok)));
     // mixer: latent attention
@@ -290,7 +318,7 @@ int step_body(b200_dlm* h, int n_tok, int n_want, int max_ctx, float* logits_out
                 h->cap, r, meta + h->off_slot, meta + h->off_pos, n_tok, c.norm_eps));
     // query folded through W_uk (and the score scale): qa[t][h][:] = scale * q[t][h][:] . W_uk[h]
     TIMED(CLS_FOLD, B200_TRY(head_gemm(st, proj + L.off_q, (long long)L.ldp, (long long)dk, static_cast<const T*>(L.ukT), (long long)dk, (long long)r * dk, h->qa,
-                     (long long)H * r, (long long)r, n_tok, r, dk, H, L.c.scale, h->attn_tc != 0)));
+                     (long long)H * r, (long long)r, n_tok, r, dk, H, L.c.a.scale, h->attn_tc != 0)));
     TIMED(CLS_ATTN, B200_TRY(attention<T>(h, L, max_ctx)));
     // values: o[t][h][:] = W_uv[h] . (sum_j p_j c_j)
     T* ob = static_cast<T*>(h->obuf);
@@ -330,6 +358,387 @@ int step_body(b200_dlm* h, int n_tok, int n_want, int max_ctx, float* logits_out
   return check_launch("decoder LM step");
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Sandwich block: norm -> (canon convolution) -> mixer -> norm -> residual, then norm -> feed-forward -> norm -> residual
+// ---------------------------------------------------------------------------------------------------------------------------
+
+// a small tensor of any shape as fp32
+int get_f32_shaped(b200_dlm* h, const std::string& name, std::vector<int64_t> shape, float** out) {
+  const Tensor* t = nullptr;
+  B200_TRY(find_tensor(h, name, shape, &t));
+  B200_TRY(h->weights.alloc_t(out, (size_t)t->numel(), false));
+  h->weight_bytes += t->numel() * 4;
+  return convert_into(t, *out);
+}
+
+__global__ void fold_head_mix_kernel(const float* __restrict__ talk, const float* __restrict__ temp, float scale, float* __restrict__ out, int H) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < H * H) out[i] = talk[i] * temp[i % H] * scale;
+}
+
+// rotary frequencies base^(-2i/dims), rescaled by wavelength (short waves kept, long waves divided by `factor`, linear blend between)
+std::vector<double> rotary_frequencies(const b200_dlm_mixer& m) {
+  const int half = m.rot_dims / 2;
+  std::vector<double> f((size_t)std::max(half, 1), 0.0);
+  const double two_pi = 6.283185307179586476925;
+  for (int i = 0; i < half; ++i) {
+    double v = std::pow((double)m.rot_base, -2.0 * i / m.rot_dims);
+    if (m.rot_factor > 0.f) {
+      const double wave = two_pi / v, orig = m.rot_original;
+      if (wave < orig / m.rot_high) {
+      } else if (wave > orig / m.rot_low) {
+        v /= m.rot_factor;
+      } else {
+        const double sm = (orig / wave - m.rot_low) / ((double)m.rot_high - m.rot_low);
+        v = (1.0 - sm) * v / m.rot_factor + sm * v;
+      }
+    }
+    f[i] = v;
+  }
+  return f;
+}
+
+size_t window_attn_smem(const b200_dlm_mixer& m, int QT, int KT, size_t es, int* kstride) {
+  const size_t Nq = (size_t)m.heads * m.dim, Nk = (size_t)m.kv_heads * m.dim, Nv = (size_t)m.kv_heads * m.vdim, rows = (size_t)QT * m.heads;
+  const size_t words = ((Nk * es + 3) / 4) | 1;           // an odd number of 32-bit words between staged key rows
+  *kstride = (int)(words * 4 / es);
+  return 4 * (QT * Nq + rows * m.vdim + 2 * rows * (KT + 1) + (size_t)m.heads * m.heads + 3 * rows) + es * ((size_t)KT * *kstride + KT * Nv) + 16;
+}
+
+int add_sig(b200_dlm* h, int H, int rpt) {
+  for (size_t k = 0; k < h->sigs.size(); ++k) if (h->sigs[k].H == H && h->sigs[k].rpt == rpt) return (int)k;
+  TileSig s; s.H = H; s.rpt = rpt; h->sigs.push_back(s);
+  return (int)h->sigs.size() - 1;
+}
+
+int finalize_sandwich_layer(b200_dlm* h, int i, std::vector<void*>& drop) {
+  Layer& L = h->layers[i];
+  const b200_dlm_config& c = h->cfg;
+  const int64_t W = c.width;
+  const size_t es = esize(h);
+  const std::string p = "l" + std::to_string(i) + ".";
+  auto matrix = [&](const std::string& name, int64_t rows, int64_t K, void** out) -> int {
+    B200_TRY(h->weights.alloc(out, (size_t)rows * K * es, false));
+    h->weight_bytes += rows * K * es;
+    return put_matrix(h, name, rows, K, *out);
+  };
+  B200_TRY(get_f32(h, p + "norm1", W, &L.n1w));
+  B200_TRY(get_f32(h, p + "norm1b", W, &L.n1bw));
+  if (c.canon_taps > 0) B200_TRY(get_f32_shaped(h, p + "canon1", {W, c.canon_taps}, &L.canon));
+  void* cat = nullptr;
+  auto at = [&](int off) { return static_cast<char*>(cat) + (size_t)off * W * es; };
+  if (L.c.mixer == B200_MIXER_PARALLEL) {
+    const b200_dlm_mixer &a = L.c.a, &b = L.c.b;
+    const std::string l = p + "mix.left.", r = p + "mix.right.";
+    L.Nq = a.heads * a.dim; L.Nk = a.kv_heads * a.dim; L.Nv = a.kv_heads * a.vdim;
+    const int Rq = b.heads * b.dim, Rv = b.heads * b.vdim;
+    const Tensor* a1 = h->store.find(r + "a1");
+    if (!a1 || a1->shape.size() != 2 || a1->shape[1] != W) B200_FAIL(B200_ERR_MISSING, "decoder LM finalize: tensor '%sa1' [rank, width] was not loaded", r.c_str());
+    L.decay_rank = (int)a1->shape[0];
+    L.a_q = 0; L.a_k = L.Nq; L.a_v = L.a_k + L.Nk;
+    L.r_q = L.a_v + L.Nv; L.r_k = L.r_q + Rq; L.r_v = L.r_k + Rq; L.r_g = L.r_v + Rv; L.r_a1 = (L.r_g + Rv + 7) / 8 * 8;    // the decay's inner projection starts on 16 bytes
+    L.ncat = L.r_a1 + L.decay_rank;
+    L.ldp = (L.ncat + 7) / 8 * 8;
+    B200_TRY(h->weights.alloc(&cat, (size_t)L.ncat * W * es, true));
+    B200_TRY(put_matrix(h, l + "q", L.Nq, W, at(L.a_q)));
+    B200_TRY(put_matrix(h, l + "k", L.Nk, W, at(L.a_k)));
+    B200_TRY(put_matrix(h, l + "v", L.Nv, W, at(L.a_v)));
+    B200_TRY(put_matrix(h, r + "q", Rq, W, at(L.r_q)));
+    B200_TRY(put_matrix(h, r + "k", Rq, W, at(L.r_k)));
+    B200_TRY(put_matrix(h, r + "v", Rv, W, at(L.r_v)));
+    B200_TRY(put_matrix(h, r + "g", Rv, W, at(L.r_g)));
+    B200_TRY(put_matrix(h, r + "a1", L.decay_rank, W, at(L.r_a1)));
+    B200_TRY(seal_weight(h, L.cat, cat, L.ncat, (int)W, drop));
+    // left: window attention
+    B200_TRY(get_f32(h, l + "q.norm", L.Nq, &L.qnorm));
+    B200_TRY(get_f32(h, l + "k.norm", L.Nk, &L.knorm));
+    if (a.conv_taps > 1) {
+      const int C = L.Nq + L.Nk + L.Nv, taps = a.conv_taps;
+      B200_TRY(h->weights.alloc_t(&L.qkv_conv, (size_t)C * taps, false));
+      const Tensor* t = nullptr;
+      int off = 0;
+      for (const char* nm : {"q", "k", "v"}) {
+        const int rows = nm[0] == 'q' ? L.Nq : nm[0] == 'k' ? L.Nk : L.Nv;
+        B200_TRY(find_tensor(h, l + nm + ".conv", {rows, taps}, &t));
+        B200_TRY(convert_into(t, L.qkv_conv + (size_t)off * taps));
+        off += rows;
+      }
+      h->weight_bytes += (int64_t)C * taps * 4;
+    }
+    float *talk = nullptr, *temp = nullptr;
+    B200_TRY(get_f32_shaped(h, l + "talk", {a.heads, a.heads}, &talk));
+    B200_TRY(get_f32(h, l + "temp", a.heads, &temp));
+    B200_TRY(get_f32(h, l + "sink", a.heads, &L.sink));
+    B200_TRY(h->weights.alloc_t(&L.mixhh, (size_t)a.heads * a.heads, false));
+    B200_LAUNCH(fold_head_mix_kernel, ceil_div(a.heads * a.heads, 256), 256, 0, nullptr, talk, temp, a.scale, L.mixhh, a.heads);
+    B200_TRY(check_launch("fold_head_mix"));
+    const std::vector<double> fr = rotary_frequencies(a);
+    B200_TRY(h->weights.alloc_t(&L.freq, fr.size(), false));
+    B200_CUDA(cudaMemcpy(L.freq, fr.data(), fr.size() * sizeof(double), cudaMemcpyHostToDevice));
+    void* wo = nullptr;
+    B200_TRY(matrix(l + "o", W, (int64_t)a.heads * a.vdim, &wo));
+    h->weight_bytes -= W * a.heads * a.vdim * es;
+    B200_TRY(seal_weight(h, L.a_o, wo, (int)W, a.heads * a.vdim, drop, (int)W));
+    B200_TRY(get_f32(h, l + "out", W, &L.a_out));
+    B200_TRY(get_f32(h, r + "out", W, &L.b_out));
+    // tile of query tokens and of keys that fits shared memory
+    L.QT = 0;
+    for (int kt : {32, 16, 8}) {
+      for (int qt : {4, 2, 1}) {
+        int ks = 0;
+        const size_t sm = window_attn_smem(a, qt, kt, es, &ks);
+        if (sm <= 200 * 1024) { L.QT = qt; L.KT = kt; L.kstride = ks; L.attn_smem = sm; break; }
+      }
+      if (L.QT) break;
+    }
+    if (!L.QT) B200_FAIL(B200_ERR_SHAPE, "decoder LM: layer %d: the window attention's heads do not fit shared memory", i);
+    L.sig = add_sig(h, a.heads, L.QT * a.heads);
+    // right: gated linear attention
+    B200_TRY(matrix(r + "a2", Rq, L.decay_rank, &L.a2));
+    B200_TRY(get_f32(h, r + "a2.b", Rq, &L.a2b));
+    B200_TRY(get_f32(h, r + "norm", b.vdim, &L.rnorm));
+    void* wo2 = nullptr;
+    B200_TRY(matrix(r + "o", W, Rv, &wo2));
+    h->weight_bytes -= W * Rv * es;
+    B200_TRY(seal_weight(h, L.r_o, wo2, (int)W, Rv, drop, (int)W));
+  } else {      // B200_MIXER_MLSTM
+    const b200_dlm_mixer& a = L.c.a;
+    const std::string m = p + "mix.";
+    const int Rq = a.heads * a.dim, Rv = a.heads * a.vdim;
+    L.r_q = 0; L.r_k = Rq; L.r_v = 2 * Rq; L.r_g = L.r_v + Rv; L.ncat = L.r_g + Rv;
+    L.ldp = (L.ncat + 7) / 8 * 8;
+    B200_TRY(h->weights.alloc(&cat, (size_t)L.ncat * W * es, false));
+    B200_TRY(put_matrix(h, m + "q", Rq, W, at(L.r_q)));
+    B200_TRY(put_matrix(h, m + "k", Rq, W, at(L.r_k)));
+    B200_TRY(put_matrix(h, m + "v", Rv, W, at(L.r_v)));
+    B200_TRY(put_matrix(h, m + "g", Rv, W, at(L.r_g)));
+    B200_TRY(seal_weight(h, L.cat, cat, L.ncat, (int)W, drop));
+    B200_TRY(h->weights.alloc(&L.w_if, (size_t)2 * a.heads * W * es, false));
+    B200_TRY(put_matrix(h, m + "i", a.heads, W, L.w_if));
+    B200_TRY(put_matrix(h, m + "f", a.heads, W, static_cast<char*>(L.w_if) + (size_t)a.heads * W * es));
+    h->weight_bytes += 2 * a.heads * W * es;
+    B200_TRY(h->weights.alloc_t(&L.if_b, (size_t)2 * a.heads, false));
+    const Tensor* t = nullptr;
+    B200_TRY(find_tensor(h, m + "i.b", {a.heads}, &t));
+    B200_TRY(convert_into(t, L.if_b));
+    B200_TRY(find_tensor(h, m + "f.b", {a.heads}, &t));
+    B200_TRY(convert_into(t, L.if_b + a.heads));
+    B200_TRY(get_f32(h, m + "norm", Rv, &L.rnorm));
+    void* wo = nullptr;
+    B200_TRY(matrix(m + "o", W, Rv, &wo));
+    h->weight_bytes -= W * Rv * es;
+    B200_TRY(seal_weight(h, L.r_o, wo, (int)W, Rv, drop, (int)W));
+  }
+  if (L.c.mlp == B200_MLP_MOE_RELU2) {
+    const int64_t E = L.c.experts, F = L.c.ff;
+    B200_TRY(get_f32(h, p + "norm2", W, &L.n2w));
+    B200_TRY(get_f32(h, p + "norm2b", W, &L.n2bw));
+    B200_TRY(matrix(p + "mlp.router", E, W, &L.router));
+    B200_TRY(h->weights.alloc(&L.ups, (size_t)E * F * W * es, false));
+    B200_TRY(h->weights.alloc(&L.downs, (size_t)E * W * F * es, false));
+    for (int64_t e = 0; e < E; ++e) {
+      const std::string q = p + "mlp.e" + std::to_string(e) + ".";
+      B200_TRY(put_matrix(h, q + "up", F, W, static_cast<char*>(L.ups) + (size_t)e * F * W * es));
+      B200_TRY(put_matrix(h, q + "down", W, F, static_cast<char*>(L.downs) + (size_t)e * W * F * es));
+    }
+    h->weight_bytes += 2 * E * F * W * es;
+  }
+  return B200_OK;
+}
+
+template <typename T>
+int small_proj(b200_dlm* h, const T* x, long long ldx, const void* w, const float* b, float* out, int M, int N, int K) {
+  B200_LAUNCH(small_proj_f32_kernel<T>, M, 256, (size_t)K * 4, h->stream, x, ldx, static_cast<const T*>(w), b, out, N, K);
+  return check_launch("small_proj_f32");
+}
+
+template <typename T, int MODE>
+int launch_scan(cudaStream_t st, const ScanParams& p, int n_entries) {
+  const dim3 grid(n_entries * p.heads, ceil_div(p.vdim, 16));
+  const size_t smem = (size_t)(3 * 8 * p.dim + 8 * 16 + 8 * 2) * 4;
+  if (p.dim <= 32) B200_LAUNCH((matrix_memory_scan_kernel<T, MODE, 4>), grid, 128, smem, st, p);
+  else if (p.dim <= 64) B200_LAUNCH((matrix_memory_scan_kernel<T, MODE, 8>), grid, 128, smem, st, p);
+  else if (p.dim <= 128) B200_LAUNCH((matrix_memory_scan_kernel<T, MODE, 16>), grid, 128, smem, st, p);
+  else B200_LAUNCH((matrix_memory_scan_kernel<T, MODE, 32>), grid, 128, smem, st, p);
+  return check_launch("matrix_memory_scan");
+}
+
+template <typename T>
+int window_attention(b200_dlm* h, const Layer& L, int n_tok, int max_ctx) {
+  const b200_dlm_mixer& a = L.c.a;
+  const TileSig& s = h->sigs[L.sig];
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA(cudaFuncSetAttribute(window_attn_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr_set = true;
+  }
+  WindowAttnParams p;
+  p.q = h->qkv32; p.ldq = L.Nq + L.Nk + L.Nv; p.kcache = L.kcache; p.vcache = L.vcache; p.mix = L.mixhh; p.sink = L.sink;
+  p.tile_row0 = h->meta_dev + s.off_row0; p.tile_rows = h->meta_dev + s.off_rows; p.tile_slot = h->meta_dev + s.off_slot;
+  p.tok_pos = h->meta_dev + h->off_pos; p.out = h->obuf; p.part = h->part;
+  p.cap = h->cap; p.H = a.heads; p.G = a.kv_heads; p.dim = a.dim; p.vdim = a.vdim; p.window = a.window; p.QT = L.QT; p.KT = L.KT; p.kstride = L.kstride;
+  // keys are cut over several CTAs per tile when the tiles alone cannot fill the GPU (decoding, short portions)
+  const int key_tiles = ceil_div(std::min(a.window, max_ctx) + L.QT - 1, L.KT);
+  int nsplit = 1;
+  if (h->attn_split > 0) nsplit = std::min(h->attn_split, 64);
+  else if (s.count < 148) nsplit = std::min(std::max(296 / std::max(s.count, 1), 1), 64);
+  nsplit = std::max(1, std::min(nsplit, key_tiles));
+  const int rpt = L.QT * a.heads;
+  while (nsplit > 1 && (size_t)s.count * nsplit * rpt * (a.vdim + 2) > h->part_floats) --nsplit;
+  p.nsplit = nsplit;
+  B200_LAUNCH(window_attn_kernel<T>, dim3(s.count, nsplit), 256, L.attn_smem, h->stream, p);
+  B200_TRY(check_launch("window_attn"));
+  if (nsplit > 1) {
+    float* merged = h->f32 ? static_cast<float*>(h->obuf) : h->attn32;
+    B200_LAUNCH(latent_attn_merge_kernel, dim3(s.count, rpt), 128, 0, h->stream, h->part, p.tile_row0, p.tile_rows, merged, a.vdim, nsplit, rpt);
+    B200_TRY(check_launch("window_attn merge"));
+    if (!h->f32) {
+      const long long n = (long long)n_tok * a.heads * a.vdim;
+      B200_LAUNCH(rows_from_f32_kernel<T>, (unsigned)ceil_div64(n, 256), 256, 0, h->stream, merged, static_cast<T*>(h->obuf), n);
+      B200_TRY(check_launch("rows_from_f32"));
+    }
+  }
+  return B200_OK;
+}
+
+// routed experts on the rows of hb -> yexp [tokens * top][W] (row t * top + k = the k-th chosen expert's output for token t)
+template <typename T>
+int routed_experts(b200_dlm* h, const Layer& L, const T* hb, int n_tok) {
+  const int W = h->cfg.width, E = L.c.experts, top = L.c.top, F = L.c.ff, pairs = n_tok * top;
+  cudaStream_t st = h->stream;
+  B200_TRY(small_proj<T>(h, hb, W, L.router, nullptr, h->route32, n_tok, E, W));
+  B200_LAUNCH(moe_route_kernel, ceil_div(n_tok, 4), 128, 0, st, h->route32, E, top, h->moe_idx, h->moe_w, n_tok);
+  B200_LAUNCH(moe_group_kernel, 1, 1024, (size_t)2 * E * sizeof(int), st, h->moe_idx, pairs, top, E, h->moe_rank, h->moe_perm, h->moe_row_tok,
+              h->moe_tile_e, h->moe_tile_r0, h->moe_tile_n, h->moe_ntiles);
+  B200_TRY(check_launch("moe route / group"));
+  const int max_tiles = ceil_div(pairs, 64) + std::min(E, pairs);
+  T* act = static_cast<T*>(h->act);
+  T* yexp = static_cast<T*>(h->yexp);
+  const T* ups = static_cast<const T*>(L.ups);
+  const T* downs = static_cast<const T*>(L.downs);
+  bool mma = false;
+  if constexpr (sizeof(T) == 2) mma = h->attn_tc && W % 16 == 0 && F % 16 == 0;
+  if (mma) {
+    if constexpr (sizeof(T) == 2) {
+      B200_LAUNCH(grouped_gemm_mma_kernel, dim3(ceil_div(F, 64), max_tiles), 128, 0, st, hb, (long long)W, h->moe_row_tok, ups, (long long)W, (long long)F * W,
+                  act, (long long)F, (const int*)nullptr, h->moe_tile_e, h->moe_tile_r0, h->moe_tile_n, h->moe_ntiles, F, W, 1);
+      B200_LAUNCH(grouped_gemm_mma_kernel, dim3(ceil_div(W, 64), max_tiles), 128, 0, st, act, (long long)F, (const int*)nullptr, downs, (long long)F, (long long)W * F,
+                  yexp, (long long)W, h->moe_perm, h->moe_tile_e, h->moe_tile_r0, h->moe_tile_n, h->moe_ntiles, W, F, 0);
+    }
+  } else {
+    B200_LAUNCH((grouped_gemm_kernel<T, T, T>), dim3(ceil_div(F, 64), max_tiles), 256, 0, st, hb, (long long)W, h->moe_row_tok, ups, (long long)W, (long long)F * W,
+                act, (long long)F, (const int*)nullptr, h->moe_tile_e, h->moe_tile_r0, h->moe_tile_n, h->moe_ntiles, F, W, 1);
+    B200_LAUNCH((grouped_gemm_kernel<T, T, T>), dim3(ceil_div(W, 64), max_tiles), 256, 0, st, act, (long long)F, (const int*)nullptr, downs, (long long)F, (long long)W * F,
+                yexp, (long long)W, h->moe_perm, h->moe_tile_e, h->moe_tile_r0, h->moe_tile_n, h->moe_ntiles, W, F, 0);
+  }
+  return check_launch("grouped expert products");
+}
+
+template <typename T>
+int step_sandwich(b200_dlm* h, int n_tok, int n_want, int max_ctx, float* logits_out) {
+  const b200_dlm_config& c = h->cfg;
+  const int W = c.width;
+  cudaStream_t st = h->stream;
+  const int* meta = h->meta_dev;
+  const int *tok_slot = meta + h->off_slot, *tok_pos = meta + h->off_pos, *tok_first = meta + h->off_first, *tok_last = meta + h->off_last;
+  const long long stride = (long long)h->tmax * W;
+  const size_t ysm = (size_t)W * 4;
+  T* hb = static_cast<T*>(h->hbuf);
+  T* proj = static_cast<T*>(h->proj);
+  T* ob = static_cast<T*>(h->obuf);
+  T* ob2 = static_cast<T*>(h->obuf2);
+  T* mixo = static_cast<T*>(h->mixo);
+  T* mixo2 = static_cast<T*>(h->mixo2);
+  TIMED(CLS_ELEMENTWISE, B200_LAUNCH(embed_norm_kernel<T>, n_tok, 256, 0, st, meta + h->off_tok, static_cast<const T*>(h->embed), c.vocab, W, h->embw,
+                                     h->layers[0].n1w, h->xin, h->h32, c.norm_eps, h->err));
+  for (int li = 0; li < c.n_layers; ++li) {
+    const Layer& L = h->layers[li];
+    const bool last = li + 1 == c.n_layers;
+    const bool mlp = L.c.mlp != B200_MLP_NONE;
+    // what the mixer reads: h + conv(h) over time
+    if (c.canon_taps > 0) {
+      TIMED(CLS_ELEMENTWISE, B200_LAUNCH((causal_conv_kernel<float, T>), n_tok, 256, 0, st, h->h32, (long long)W, L.canon_hist, L.canon, hb, (long long)W, W, c.canon_taps,
+                                         1, tok_slot, tok_pos, tok_first);
+            if (c.canon_taps > 1) B200_LAUNCH(conv_carry_kernel<float>, n_tok, 256, 0, st, h->h32, (long long)W, L.canon_hist, W, c.canon_taps - 1, tok_slot, tok_pos, tok_last));
+    } else {
+      const long long n = (long long)n_tok * W;
+      TIMED(CLS_ELEMENTWISE, B200_LAUNCH(rows_from_f32_kernel<T>, (unsigned)ceil_div64(n, 256), 256, 0, st, h->h32, hb, n));
+    }
+    TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, hb, W, L.cat, proj, L.ldp, n_tok)));
+    const float* w_after = mlp ? L.n2w : (last ? nullptr : h->layers[li + 1].n1w);      // the norm whose input this sublayer completes
+    float* trace = (h->trace_layers && !mlp) ? h->trace + (long long)li * stride : nullptr;
+    if (L.c.mixer == B200_MIXER_PARALLEL) {
+      const b200_dlm_mixer &a = L.c.a, &b = L.c.b;
+      const int C = L.Nq + L.Nk + L.Nv;
+      // left: convolution on q, k, v, then norm and rotation, keys and values into the cache
+      TIMED(CLS_ELEMENTWISE, B200_LAUNCH((causal_conv_kernel<T, float>), n_tok, 256, 0, st, proj, (long long)L.ldp, L.qkv_hist, L.qkv_conv, h->qkv32, (long long)C, C,
+                                         std::max(a.conv_taps, 1), 0, tok_slot, tok_pos, tok_first);
+            if (a.conv_taps > 1) B200_LAUNCH(conv_carry_kernel<T>, n_tok, 256, 0, st, proj, (long long)L.ldp, L.qkv_hist, C, a.conv_taps - 1, tok_slot, tok_pos, tok_last);
+            B200_LAUNCH(qk_norm_rope_kernel<T>, n_tok, 256, (size_t)a.rot_dims * 4 + 4, st, h->qkv32, (long long)C, L.Nq, L.Nk, L.Nv, a.dim, a.rot_dims / 2, L.qnorm, L.knorm, L.freq,
+                        static_cast<T*>(L.kcache), static_cast<T*>(L.vcache), h->cap, tok_slot, tok_pos, c.norm_eps));
+      TIMED(CLS_ATTN, B200_TRY(window_attention<T>(h, L, n_tok, max_ctx)));
+      TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, ob, (long long)a.heads * a.vdim, L.a_o, mixo, W, n_tok)));
+      // right: decay logits, the recurrence, head norm and gate
+      const int Rq = b.heads * b.dim, Rv = b.heads * b.vdim;
+      TIMED(CLS_FOLD, B200_TRY(head_gemm(st, proj + L.r_a1, (long long)L.ldp, 0, static_cast<const T*>(L.a2), (long long)L.decay_rank, 0, h->gate32, (long long)Rq, 0,
+                                         n_tok, Rq, L.decay_rank, 1, 1.f, h->attn_tc != 0)));
+      ScanParams sp;
+      sp.proj = proj; sp.ld = L.ldp; sp.off_q = L.r_q; sp.off_k = L.r_k; sp.off_v = L.r_v; sp.z = h->gate32; sp.zb = L.a2b;
+      sp.inv_tau = 1.f / b.tau; sp.cap = 0.f; sp.qscale = 1.f / sqrtf((float)b.dim); sp.St = L.St; sp.nvec = nullptr; sp.mval = nullptr;
+      sp.ent_tok0 = meta + h->off_ent_tok0; sp.ent_ntok = meta + h->off_ent_ntok; sp.ent_slot = meta + h->off_ent_slot; sp.ent_pos0 = meta + h->off_ent_pos0;
+      sp.out = h->scan32; sp.heads = b.heads; sp.dim = b.dim; sp.vdim = b.vdim;
+      TIMED(CLS_RECURRENT, B200_TRY((launch_scan<T, MODE_DECAY>(st, sp, h->n_entries))));
+      const long long rows = (long long)n_tok * b.heads;
+      TIMED(CLS_ELEMENTWISE, B200_LAUNCH(head_norm_gate_kernel<T>, (unsigned)ceil_div64(rows, 4), 128, 0, st, h->scan32, L.rnorm, 0, proj, (long long)L.ldp, L.r_g, 1, ob2,
+                                         b.heads, b.vdim, rows, c.norm_eps));
+      TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, ob2, (long long)Rv, L.r_o, mixo2, W, n_tok)));
+      TIMED(CLS_ELEMENTWISE, B200_LAUNCH(sublayer_end_kernel<T>, n_tok, 256, ysm, st, h->xin, mixo, L.a_out, mixo2, L.b_out, 0.5f, (const float*)nullptr, 0, L.n1bw, trace,
+                                         w_after, mlp ? nullptr : h->h32, mlp ? hb : nullptr, W, c.norm_eps));
+    } else {
+      const b200_dlm_mixer& a = L.c.a;
+      const int Rv = a.heads * a.vdim;
+      TIMED(CLS_FOLD, B200_TRY(small_proj<T>(h, hb, W, L.w_if, L.if_b, h->gate32, n_tok, 2 * a.heads, W)));
+      ScanParams sp;
+      sp.proj = proj; sp.ld = L.ldp; sp.off_q = L.r_q; sp.off_k = L.r_k; sp.off_v = L.r_v; sp.z = h->gate32; sp.zb = nullptr;
+      sp.inv_tau = 0.f; sp.cap = a.gate_cap; sp.qscale = 1.f / sqrtf((float)a.dim); sp.St = L.St; sp.nvec = L.nvec; sp.mval = L.mval;
+      sp.ent_tok0 = meta + h->off_ent_tok0; sp.ent_ntok = meta + h->off_ent_ntok; sp.ent_slot = meta + h->off_ent_slot; sp.ent_pos0 = meta + h->off_ent_pos0;
+      sp.out = h->scan32; sp.heads = a.heads; sp.dim = a.dim; sp.vdim = a.vdim;
+      TIMED(CLS_RECURRENT, B200_TRY((launch_scan<T, MODE_EXPGATE>(st, sp, h->n_entries))));
+      const long long rows = (long long)n_tok * a.heads;
+      TIMED(CLS_ELEMENTWISE, B200_LAUNCH(head_norm_gate_kernel<T>, (unsigned)ceil_div64(rows, 4), 128, 0, st, h->scan32, L.rnorm, a.vdim, proj, (long long)L.ldp, L.r_g, 0, ob2,
+                                         a.heads, a.vdim, rows, c.norm_eps));
+      TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, ob2, (long long)Rv, L.r_o, mixo, W, n_tok)));
+      TIMED(CLS_ELEMENTWISE, B200_LAUNCH(sublayer_end_kernel<T>, n_tok, 256, ysm, st, h->xin, mixo, (const float*)nullptr, (const T*)nullptr, (const float*)nullptr, 1.f,
+                                         (const float*)nullptr, 0, L.n1bw, trace, w_after, mlp ? nullptr : h->h32, mlp ? hb : nullptr, W, c.norm_eps));
+    }
+    if (mlp) {
+      TIMED(CLS_EXPERTS, B200_TRY(routed_experts<T>(h, L, hb, n_tok)));
+      TIMED(CLS_ELEMENTWISE, B200_LAUNCH(sublayer_end_kernel<T>, n_tok, 256, ysm, st, h->xin, static_cast<const T*>(h->yexp), (const float*)nullptr, (const T*)nullptr,
+                                         (const float*)nullptr, 1.f, h->moe_w, L.c.top, L.n2bw, h->trace_layers ? h->trace + (long long)li * stride : nullptr,
+                                         last ? nullptr : h->layers[li + 1].n1w, h->h32, (T*)nullptr, W, c.norm_eps));
+    }
+  }
+  B200_TRY(check_launch("decoder LM layers"));
+  if (n_want > 0) {
+    T* hf = static_cast<T*>(h->hf);
+    TIMED(CLS_ELEMENTWISE, B200_LAUNCH(rmsnorm_rows_kernel<T>, n_want, 256, 0, st, h->xin, meta + h->off_want, h->fnw, hf, W, c.norm_eps));
+    const long long n = (long long)n_want * c.vocab;
+    if (h->head.tiles) {
+      const int ldl = (c.vocab + 7) / 8 * 8;
+      TIMED(CLS_LINEAR, B200_TRY(linear<bf16>(h, reinterpret_cast<const bf16*>(hf), W, h->head, h->head_bf, ldl, n_want)));
+      B200_LAUNCH(softcap_rows_kernel, (unsigned)ceil_div64(n, 256), 256, 0, st, h->head_bf, (long long)ldl, h->logits, c.vocab, n, c.logit_softcap);
+    } else {
+      TIMED(CLS_LINEAR, B200_TRY(gemm_nt(st, hf, (long long)W, 0, static_cast<const T*>(h->head.rm), (long long)W, 0, h->logits, (long long)c.vocab, 0, n_want, c.vocab, W, 1, 1.f)));
+      if (c.logit_softcap > 0.f)
+        B200_LAUNCH(softcap_rows_kernel, (unsigned)ceil_div64(n, 256), 256, 0, st, (const bf16*)nullptr, 0LL, h->logits, c.vocab, n, c.logit_softcap);
+    }
+    if (logits_out)
+      B200_CUDA(cudaMemcpyAsync(logits_out, h->logits, (size_t)n_want * c.vocab * 4, cudaMemcpyDeviceToDevice, st));
+  }
+  return check_launch("decoder LM step");
+}
+
 }  // namespace
 
 extern "C" {
@@ -338,12 +747,36 @@ int b200_dlm_create(const b200_dlm_config* cfg, b200_dlm** out) {
   if (!cfg || !out || !cfg->layers) B200_FAIL(B200_ERR_INVALID, "dlm_create: null argument");
   if (cfg->vocab < 1 || cfg->width < 1 || cfg->n_layers < 1) B200_FAIL(B200_ERR_INVALID, "dlm_create: vocab, width and n_layers must be positive");
   if (cfg->compute_dtype != B200_BF16 && cfg->compute_dtype != B200_F32) B200_FAIL(B200_ERR_INVALID, "dlm_create: compute_dtype must be bf16 or f32");
+  if (cfg->block != B200_BLOCK_GATED_DEPTH_AVERAGE && cfg->block != B200_BLOCK_SANDWICH) B200_FAIL(B200_ERR_INVALID, "dlm_create: unknown block arrangement %d", cfg->block);
+  if (cfg->canon_taps < 0 || cfg->canon_taps > 64) B200_FAIL(B200_ERR_INVALID, "dlm_create: canon_taps must be in 0..64");
   for (int i = 0; i < cfg->n_layers; ++i) {
     const b200_dlm_layer& l = cfg->layers[i];
-    if (l.mixer != B200_MIXER_LATENT_ATTENTION) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: unknown mixer %d", i, l.mixer);
-    if (l.heads < 1 || l.dim < 1 || l.vdim < 1 || l.kv_rank < 1 || l.kv_rank > 1024)
-      B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: heads, dim, vdim must be positive and kv_rank in 1..1024", i);
-    if (l.mlp != B200_MLP_NONE && l.mlp != B200_MLP_DENSE_RELU2) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: unknown mlp kind %d", i, l.mlp);
+    const b200_dlm_mixer &a = l.a, &b = l.b;
+    if (cfg->block == B200_BLOCK_GATED_DEPTH_AVERAGE) {
+      if (l.mixer != B200_MIXER_LATENT_ATTENTION) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: mixer %d is not registered for this block arrangement", i, l.mixer);
+      if (a.heads < 1 || a.dim < 1 || a.vdim < 1 || a.kv_rank < 1 || a.kv_rank > 1024)
+        B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: heads, dim, vdim must be positive and kv_rank in 1..1024", i);
+      if (l.mlp != B200_MLP_NONE && l.mlp != B200_MLP_DENSE_RELU2) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: mlp kind %d is not registered for this block arrangement", i, l.mlp);
+    } else {
+      if (l.mixer == B200_MIXER_PARALLEL) {
+        if (a.kind != B200_MIXER_WINDOW_ATTENTION || b.kind != B200_MIXER_GLA)
+          B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: a parallel pair is window attention beside gated linear attention", i);
+        if (a.heads < 1 || a.kv_heads < 1 || a.heads % a.kv_heads || a.dim < 1 || a.vdim < 1 || a.window < 1)
+          B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: window attention wants heads a multiple of kv_heads, positive dim, vdim and window", i);
+        if (a.rot_dims < 0 || a.rot_dims % 2 || a.rot_dims > a.dim) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: rot_dims must be even and at most dim", i);
+        if (a.conv_taps < 0 || a.conv_taps > 64) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: conv_taps must be in 0..64", i);
+        if (b.heads < 1 || b.dim < 1 || b.dim > 256 || b.vdim < 1 || !(b.tau > 0.f))
+          B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: gated linear attention wants positive heads, vdim, tau and dim in 1..256", i);
+      } else if (l.mixer == B200_MIXER_MLSTM) {
+        if (a.heads < 1 || a.dim < 1 || a.dim > 256 || a.vdim < 1 || !(a.gate_cap > 0.f))
+          B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: mLSTM wants positive heads, vdim, gate_cap and dim in 1..256", i);
+      } else {
+        B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: mixer %d is not registered for this block arrangement", i, l.mixer);
+      }
+      if (l.mlp != B200_MLP_NONE && l.mlp != B200_MLP_MOE_RELU2) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: mlp kind %d is not registered for this block arrangement", i, l.mlp);
+      if (l.mlp == B200_MLP_MOE_RELU2 && (l.experts < 1 || l.experts > 4096 || l.top < 1 || l.top > l.experts || l.top > 32))
+        B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: experts in 1..4096 and top in 1..min(experts, 32)", i);
+    }
     if (l.mlp != B200_MLP_NONE && l.ff < 1) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: ff must be positive", i);
   }
   auto* h = new b200_dlm();
@@ -399,10 +832,15 @@ int b200_dlm_finalize(b200_dlm* h) {
   };
   B200_TRY(matrix("embed", c.vocab, W, &h->embed));
   h->weight_bytes += (int64_t)c.vocab * W * es;
-  for (int i = 0; i < c.n_layers; ++i) {
+  const bool sandwich = c.block == B200_BLOCK_SANDWICH;
+  if (sandwich) {
+    B200_TRY(get_f32(h, "embed.norm", W, &h->embw));
+    for (int i = 0; i < c.n_layers; ++i) B200_TRY(finalize_sandwich_layer(h, i, drop));
+  }
+  for (int i = 0; i < c.n_layers && !sandwich; ++i) {
     Layer& L = h->layers[i];
     const std::string p = "l" + std::to_string(i) + ".";
-    const int64_t H = L.c.heads, dk = L.c.dim, dv = L.c.vdim, r = L.c.kv_rank, F = L.c.ff;
+    const int64_t H = L.c.a.heads, dk = L.c.a.dim, dv = L.c.a.vdim, r = L.c.a.kv_rank, F = L.c.ff;
     const bool mlp = L.c.mlp != B200_MLP_NONE;
     B200_TRY(get_f32(h, p + "norm1", W, &L.n1w));
     B200_TRY(get_f32(h, p + "norm1.b", W, &L.n1b));
@@ -438,11 +876,11 @@ int b200_dlm_finalize(b200_dlm* h) {
     h->weight_bytes += H * dv * r * es;
     void* wo = nullptr;
     B200_TRY(matrix(p + "mix.o", W, H * dv, &wo));
-    B200_TRY(seal_weight(h, L.o, wo, (int)W, (int)(H * dv), drop));
+    B200_TRY(seal_weight(h, L.o, wo, (int)W, (int)(H * dv), drop, (int)W));
     if (mlp) {
       void* wd = nullptr;
       B200_TRY(matrix(p + "mlp.down", W, F, &wd));
-      B200_TRY(seal_weight(h, L.down, wd, (int)W, (int)F, drop));
+      B200_TRY(seal_weight(h, L.down, wd, (int)W, (int)F, drop, (int)W));
     }
     B200_TRY(get_f32(h, p + "dwa", i + 2, &L.avg));
     int sig = -1;
@@ -452,7 +890,7 @@ int b200_dlm_finalize(b200_dlm* h) {
     L.sig = sig;
   }
   B200_TRY(get_f32(h, "final.norm", W, &h->fnw));
-  B200_TRY(get_f32(h, "final.norm.b", W, &h->fnb));
+  if (!sandwich) B200_TRY(get_f32(h, "final.norm.b", W, &h->fnb));
   void* hd = nullptr;
   B200_TRY(matrix("head", c.vocab, W, &hd));
   B200_TRY(seal_weight(h, h->head, hd, c.vocab, (int)W, drop));
@@ -508,28 +946,80 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
   const size_t es = esize(h);
   const size_t T = (size_t)max_step_tokens, W = (size_t)c.width;
   h->stream = static_cast<cudaStream_t>(stream);
-  size_t max_ldp = 0, max_hr = 0, max_hv = 0, max_ff = 1, max_r = 0, max_tiles = 0;
+  const bool sandwich = c.block == B200_BLOCK_SANDWICH;
+  size_t max_ldp = 0, max_hr = 0, max_hv = 0, max_ff = 1, max_r = 0, max_tiles = 0, max_qkv = 1, max_rv = 1, max_gate = 1, max_e = 1, max_top = 0, max_part = 0;
   for (auto& L : h->layers) {
-    B200_TRY(A.alloc(&L.cache, (size_t)slots * capacity * L.c.kv_rank * es));
+    const b200_dlm_mixer &a = L.c.a, &b = L.c.b;
     max_ldp = std::max(max_ldp, (size_t)L.ldp);
-    max_hr = std::max(max_hr, (size_t)L.c.heads * L.c.kv_rank);
-    max_hv = std::max(max_hv, (size_t)L.c.heads * L.c.vdim);
+    max_hv = std::max(max_hv, (size_t)a.heads * a.vdim);
     max_ff = std::max(max_ff, (size_t)L.c.ff);
-    max_r = std::max(max_r, (size_t)L.c.kv_rank);
+    if (!sandwich) {
+      B200_TRY(A.alloc(&L.cache, (size_t)slots * capacity * a.kv_rank * es));
+      max_hr = std::max(max_hr, (size_t)a.heads * a.kv_rank);
+      max_r = std::max(max_r, (size_t)a.kv_rank);
+      continue;
+    }
+    // per request: the last inputs of the convolutions, keys and values of the window attention, the matrix memories
+    if (c.canon_taps > 1) B200_TRY(A.alloc_t(&L.canon_hist, (size_t)slots * (c.canon_taps - 1) * W));
+    if (L.c.mixer == B200_MIXER_PARALLEL) {
+      const size_t C = (size_t)L.Nq + L.Nk + L.Nv;
+      if (a.conv_taps > 1) B200_TRY(A.alloc_t(&L.qkv_hist, (size_t)slots * (a.conv_taps - 1) * C));
+      B200_TRY(A.alloc(&L.kcache, (size_t)slots * capacity * L.Nk * es));
+      B200_TRY(A.alloc(&L.vcache, (size_t)slots * capacity * L.Nv * es));
+      B200_TRY(A.alloc_t(&L.St, (size_t)slots * b.heads * b.vdim * b.dim));
+      max_qkv = std::max(max_qkv, C);
+      max_rv = std::max(max_rv, (size_t)b.heads * b.vdim);
+      max_gate = std::max(max_gate, (size_t)b.heads * b.dim);
+      max_part = std::max(max_part, (size_t)L.QT * a.heads * (a.vdim + 2));
+    } else {
+      const size_t slices = (size_t)ceil_div(a.vdim, 16);
+      B200_TRY(A.alloc_t(&L.St, (size_t)slots * a.heads * a.vdim * a.dim));
+      B200_TRY(A.alloc_t(&L.nvec, (size_t)slots * a.heads * slices * a.dim));
+      B200_TRY(A.alloc_t(&L.mval, (size_t)slots * a.heads * slices));
+      max_rv = std::max(max_rv, (size_t)a.heads * a.vdim);
+      max_gate = std::max(max_gate, (size_t)2 * a.heads);
+    }
+    if (L.c.mlp == B200_MLP_MOE_RELU2) { max_e = std::max(max_e, (size_t)L.c.experts); max_top = std::max(max_top, (size_t)L.c.top); }
   }
   B200_TRY(A.alloc_t(&h->xin, T * W));
-  B200_TRY(A.alloc_t(&h->stack, (size_t)(c.n_layers + 1) * T * W));
+  if (!sandwich) {
+    B200_TRY(A.alloc_t(&h->stack, (size_t)(c.n_layers + 1) * T * W));
+    B200_TRY(A.alloc_t(&h->qa, T * max_hr));
+    B200_TRY(A.alloc_t(&h->ol, T * max_hr));
+    h->part_floats = (size_t)600 * 16 * (max_r + 2);
+    B200_TRY(A.alloc(&h->ffo, T * W * es));
+  } else {
+    B200_TRY(A.alloc_t(&h->h32, T * W));
+    B200_TRY(A.alloc_t(&h->qkv32, T * max_qkv));
+    B200_TRY(A.alloc_t(&h->scan32, T * max_rv));
+    B200_TRY(A.alloc_t(&h->gate32, T * max_gate));
+    B200_TRY(A.alloc_t(&h->attn32, T * max_hv));
+    B200_TRY(A.alloc(&h->obuf2, T * max_rv * es));
+    B200_TRY(A.alloc(&h->mixo2, T * W * es));
+    h->part_floats = (size_t)600 * std::max(max_part, (size_t)1);
+    if (max_top) {
+      const size_t pairs = T * max_top, tiles = pairs / 64 + max_e + 2;
+      B200_TRY(A.alloc_t(&h->route32, T * max_e));
+      B200_TRY(A.alloc_t(&h->moe_w, pairs));
+      B200_TRY(A.alloc_t(&h->moe_idx, pairs));
+      B200_TRY(A.alloc_t(&h->moe_rank, pairs));
+      B200_TRY(A.alloc_t(&h->moe_perm, pairs));
+      B200_TRY(A.alloc_t(&h->moe_row_tok, pairs));
+      B200_TRY(A.alloc_t(&h->moe_tile_e, tiles));
+      B200_TRY(A.alloc_t(&h->moe_tile_r0, tiles));
+      B200_TRY(A.alloc_t(&h->moe_tile_n, tiles));
+      B200_TRY(A.alloc_t(&h->moe_ntiles, 1));
+      B200_TRY(A.alloc(&h->yexp, pairs * W * es));
+      max_ff *= max_top;        // the experts' hidden rows: one per (token, chosen expert)
+    }
+  }
   if (h->trace_layers) B200_TRY(A.alloc_t(&h->trace, (size_t)c.n_layers * T * W));
-  B200_TRY(A.alloc_t(&h->qa, T * max_hr));
-  B200_TRY(A.alloc_t(&h->ol, T * max_hr));
-  h->part_floats = (size_t)600 * 16 * (max_r + 2);
   B200_TRY(A.alloc_t(&h->part, h->part_floats));
   B200_TRY(A.alloc(&h->hbuf, T * W * es));
   B200_TRY(A.alloc(&h->proj, T * max_ldp * es));
   B200_TRY(A.alloc(&h->obuf, T * max_hv * es));
   B200_TRY(A.alloc(&h->mixo, T * W * es));
   B200_TRY(A.alloc(&h->act, T * max_ff * es));
-  B200_TRY(A.alloc(&h->ffo, T * W * es));
   B200_TRY(A.alloc(&h->hf, (size_t)max_want * W * es));
   B200_TRY(A.alloc_t(&h->logits, (size_t)max_want * c.vocab));
   B200_TRY(A.alloc_t(&h->logits_bf, (size_t)max_want * c.vocab));
@@ -543,6 +1033,13 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
   h->off_slot = off; off += max_step_tokens;
   h->off_pos = off; off += max_step_tokens;
   h->off_want = off; off += max_want;
+  h->off_first = off; off += max_step_tokens;
+  h->off_last = off; off += max_step_tokens;
+  const int max_entries = std::min(slots, max_step_tokens);
+  h->off_ent_tok0 = off; off += max_entries;
+  h->off_ent_ntok = off; off += max_entries;
+  h->off_ent_slot = off; off += max_entries;
+  h->off_ent_pos0 = off; off += max_entries;
   for (auto& s : h->sigs) {
     max_tiles = (size_t)ceil_div64((int64_t)max_step_tokens * s.H, s.rpt) + (size_t)std::min(slots, max_step_tokens);
     s.off_row0 = off; off += (int)max_tiles;
@@ -608,17 +1105,24 @@ int b200_dlm_step(b200_dlm* h, int n_entries, const int32_t* slots_host, const i
         ++sg.count;
       }
     }
+    m[h->off_ent_tok0 + e] = t; m[h->off_ent_ntok + e] = n; m[h->off_ent_slot + e] = s; m[h->off_ent_pos0 + e] = base;
+    const int first = t, lastt = t + n - 1;
     for (int i = 0; i < n; ++i, ++t) {
       m[h->off_tok + t] = tokens_host[t];
       m[h->off_slot + t] = s;
       m[h->off_pos + t] = base + i;
+      m[h->off_first + t] = first;
+      m[h->off_last + t] = lastt;
     }
     max_ctx = std::max(max_ctx, base + n);
   }
   for (int i = 0; i < n_want; ++i) m[h->off_want + i] = want_host[i];
   B200_CUDA(cudaMemcpyAsync(h->meta_dev, m, (size_t)h->meta_ints * sizeof(int), cudaMemcpyHostToDevice, h->stream));
   B200_CUDA(cudaEventRecord(h->ev_meta, h->stream));
-  const int rc = h->f32 ? step_body<float>(h, t, n_want, max_ctx, logits_dev) : step_body<bf16>(h, t, n_want, max_ctx, logits_dev);
+  h->n_entries = n_entries;
+  int rc;
+  if (h->cfg.block == B200_BLOCK_SANDWICH) rc = h->f32 ? step_sandwich<float>(h, t, n_want, max_ctx, logits_dev) : step_sandwich<bf16>(h, t, n_want, max_ctx, logits_dev);
+  else rc = h->f32 ? step_body<float>(h, t, n_want, max_ctx, logits_dev) : step_body<bf16>(h, t, n_want, max_ctx, logits_dev);
   if (rc != B200_OK) return rc;
   if (h->time_kernels && h->ev_used) {      // diagnostics only: waits for the step and sums its intervals per class
     B200_CUDA(cudaStreamSynchronize(h->stream));
@@ -689,9 +1193,9 @@ int b200_dlm_read_buffer(b200_dlm* h, const char* name, void* dst_dev, int64_t c
   B200_FAIL(B200_ERR_INVALID, "dlm_read_buffer: unknown buffer '%s'", name);
 }
 
-int b200_dlm_read_timers(b200_dlm* h, double* ms4_host, int reset) {
-  if (!h || !ms4_host) B200_FAIL(B200_ERR_INVALID, "dlm_read_timers: null argument");
-  for (int i = 0; i < 4; ++i) { ms4_host[i] = h->class_ms[i]; if (reset) h->class_ms[i] = 0; }
+int b200_dlm_read_timers(b200_dlm* h, double* ms6_host, int reset) {
+  if (!h || !ms6_host) B200_FAIL(B200_ERR_INVALID, "dlm_read_timers: null argument");
+  for (int i = 0; i < 6; ++i) { ms6_host[i] = h->class_ms[i]; if (reset) h->class_ms[i] = 0; }
   return B200_OK;
 }
 
@@ -699,7 +1203,7 @@ int b200_dlm_read_timers(b200_dlm* h, double* ms4_host, int reset) {
 int64_t b200_dlm_algorithmic_bytes(b200_dlm* h, int tokens, int context) {
   if (!h) return 0;
   int64_t b = h->weight_bytes - (int64_t)h->cfg.vocab * h->cfg.width * esize(h);     // the embedding is gathered, not streamed
-  for (auto& L : h->layers) b += ((int64_t)context + tokens) * L.c.kv_rank * esize(h);
+  for (auto& L : h->layers) b += ((int64_t)context + tokens) * L.c.a.kv_rank * esize(h);
   return b + (int64_t)tokens * h->cfg.width * esize(h);
 }
 
@@ -709,7 +1213,7 @@ int64_t b200_dlm_algorithmic_flops(b200_dlm* h, int tokens, int context) {
   const int64_t T = tokens, W = h->cfg.width;
   int64_t f = 0;
   for (auto& L : h->layers) {
-    const int64_t H = L.c.heads, dk = L.c.dim, dv = L.c.vdim, r = L.c.kv_rank;
+    const int64_t H = L.c.a.heads, dk = L.c.a.dim, dv = L.c.a.vdim, r = L.c.a.kv_rank;
     f += 2 * T * W * L.ncat + 2 * T * H * dk * r + 2 * T * H * dv * r + 2 * T * W * H * dv;
     if (L.c.mlp != B200_MLP_NONE) f += 2 * T * W * L.c.ff;
     f += 4 * H * r * (T * context + T * (T + 1) / 2);

@@ -1,0 +1,714 @@
+// Further mechanisms of the decoder-LM handle (dlm.cu), first used by the Govuvik design: RMS-norm sandwiches around every
+// sublayer, per-channel causal convolutions with carried inputs, rotary positions with wavelength-dependent rescaling,
+// sliding-window attention whose heads' scores are mixed before the softmax (with a sink), two recurrent matrix memories
+// (per-channel decay; stabilised exponential gates), and a routed mixture of experts.
+//   T = activation / weight / cache type (bf16, or float in the all-fp32 mode).  Norms, positions and angles, scores and
+//   softmax, routers, gates, decays, the recurrent state and the residual stream are fp32 in both modes.
+#pragma once
+
+#include "dlm_kernels.cuh"
+
+namespace b200 {
+namespace dlm {
+
+__device__ __forceinline__ float siluf(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float log_sigmoidf(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+// rms-normalises one fp32 row held in shared memory (or global): returns 1 / sqrt(mean(x^2) + eps)
+__device__ __forceinline__ float block_rrms(const float* __restrict__ x, int W, float eps, float* red) {
+  float s = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) s += x[i] * x[i];
+  return 1.f / sqrtf(block_sum(s, red) / (float)W + eps);
+}
+
+// x = rms_norm(table[token]) * w_embed -> residual stream; h = rms_norm(x) * w_next -> what the first layer reads (fp32)
+template <typename T>
+__global__ void __launch_bounds__(256) embed_norm_kernel(const int* __restrict__ tokens, const T* __restrict__ table, int vocab, int W,
+                                                         const float* __restrict__ w_embed, const float* __restrict__ w_next,
+                                                         float* __restrict__ xin, float* __restrict__ h, float eps, int* __restrict__ err) {
+  __shared__ float red[32];
+  const long long t = blockIdx.x;
+  int id = tokens[t];
+  const bool bad = id < 0 || id >= vocab;
+  if (bad) { if (threadIdx.x == 0) atomicOr(err, ERR_TOKEN); id = 0; }
+  const T* row = table + (long long)id * W;
+  float* x = xin + t * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) x[i] = bad ? 0.f : to_f(row[i]);
+  __syncthreads();
+  const float r0 = block_rrms(x, W, eps, red);
+  __syncthreads();
+  for (int i = threadIdx.x; i < W; i += blockDim.x) x[i] = x[i] * r0 * w_embed[i];
+  __syncthreads();
+  const float r1 = block_rrms(x, W, eps, red);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) h[t * W + i] = x[i] * r1 * w_next[i];
+}
+
+// out[row] = rms_norm(x[rows ? rows[row] : row]) * w
+template <typename T>
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+                                                           T* __restrict__ out, int W, float eps) {
+  __shared__ float red[32];
+  const long long src = rows ? rows[blockIdx.x] : blockIdx.x;
+  const float* xr = x + src * W;
+  const float r = block_rrms(xr, W, eps, red);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) out[(long long)blockIdx.x * W + i] = from_f<T>(xr[i] * r * w[i]);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Causal convolution over time on every channel, with the last taps - 1 inputs of a sequence carried between steps.
+//   y[t][c] = (residual ? u[t][c] : 0) + sum_j w[c][j] * u[t - taps + 1 + j][c],  inputs before position 0 are zero
+// The step's tokens are rows of `in`; a tap that reaches in front of the step's first token of the request reads the carried
+// inputs hist[slot][p mod (taps - 1)][c] (p = absolute position).  The carried inputs are written by conv_carry_kernel AFTER
+// this kernel, so that no token of the step reads a row that another one has replaced.
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) causal_conv_kernel(const TI* __restrict__ in, long long ld_in, const float* __restrict__ hist,
+                                                          const float* __restrict__ w, TO* __restrict__ out, long long ld_out, int C,
+                                                          int taps, int residual, const int* __restrict__ tok_slot,
+                                                          const int* __restrict__ tok_pos, const int* __restrict__ tok_first) {
+  const long long t = blockIdx.x;
+  const int pos = tok_pos[t], slot = tok_slot[t], back_in_step = (int)t - tok_first[t];   // tokens of this request in front of t
+  const int keep = taps - 1;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float u = to_f(in[t * ld_in + c]);
+    float acc = w[(long long)c * taps + keep] * u;
+    for (int b = 1; b <= keep; ++b) {
+      if (b > pos) break;                                  // in front of the sequence: zero
+      const float v = b <= back_in_step ? to_f(in[(t - b) * ld_in + c]) : hist[((long long)slot * keep + (pos - b) % keep) * C + c];
+      acc = fmaf(w[(long long)c * taps + keep - b], v, acc);
+    }
+    out[t * ld_out + c] = from_f<TO>(residual ? u + acc : acc);
+  }
+}
+
+// the last taps - 1 inputs of every request of the step go into its carried rows (by position mod (taps - 1))
+template <typename TI>
+__global__ void __launch_bounds__(256) conv_carry_kernel(const TI* __restrict__ in, long long ld_in, float* __restrict__ hist, int C, int keep,
+                                                         const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
+                                                         const int* __restrict__ tok_last) {
+  const long long t = blockIdx.x;
+  if (tok_last[t] - (int)t >= keep) return;                // not among the request's last taps - 1 tokens of this step
+  float* dst = hist + ((long long)tok_slot[t] * keep + tok_pos[t] % keep) * C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) dst[c] = to_f(in[t * ld_in + c]);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Query / key preparation of the window attention, one CTA per token, on the convolved projections qkv fp32 [T][Nq + Nk + Nv]:
+//   q <- rope(rms_norm(q over all Nq) * wq)   (kept in place, fp32: the scores are fp32 products)
+//   k <- rope(rms_norm(k over all Nk) * wk)   -> key cache row of the token;  v -> value cache row
+// Rotary: the first 2 * half dimensions of every head, dimension i with i + half, angle = pos * freq[i]; the angle and its sine
+// and cosine are evaluated in double once per (token, i) so that a position in the thousands costs no digits, then kept as fp32.
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) qk_norm_rope_kernel(float* __restrict__ qkv, long long ld, int Nq, int Nk, int Nv, int dim, int half,
+                                                           const float* __restrict__ wq, const float* __restrict__ wk,
+                                                           const double* __restrict__ freq, T* __restrict__ kcache, T* __restrict__ vcache,
+                                                           int cap, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos, float eps) {
+  __shared__ float red[32];
+  extern __shared__ float rot[];        // [half] cosines, [half] sines
+  const long long t = blockIdx.x;
+  float* q = qkv + t * ld;
+  float* k = q + Nq;
+  const float* v = k + Nk;
+  const int pos = tok_pos[t];
+  const long long crow = (long long)tok_slot[t] * cap + pos;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    double sn, cs;
+    sincos((double)pos * freq[i], &sn, &cs);
+    rot[i] = (float)cs; rot[half + i] = (float)sn;
+  }
+  const float rq = block_rrms(q, Nq, eps, red);
+  __syncthreads();
+  const float rk = block_rrms(k, Nk, eps, red);
+  // every (head, i < half) pair or unrotated element is owned by one thread: no hazards in place
+  for (int e = threadIdx.x; e < Nq; e += blockDim.x) {
+    const int d = e % dim;
+    if (d < half) {
+      const float cs = rot[d], sn = rot[half + d];
+      const float a = q[e] * rq * wq[e], b = q[e + half] * rq * wq[e + half];
+      q[e] = a * cs - b * sn;
+      q[e + half] = b * cs + a * sn;
+    } else if (d >= 2 * half) {
+      q[e] = q[e] * rq * wq[e];
+    }
+  }
+  T* kc = kcache + crow * Nk;
+  for (int e = threadIdx.x; e < Nk; e += blockDim.x) {
+    const int d = e % dim;
+    if (d < half) {
+      const float cs = rot[d], sn = rot[half + d];
+      const float a = k[e] * rk * wk[e], b = k[e + half] * rk * wk[e + half];
+      kc[e] = from_f<T>(a * cs - b * sn);
+      kc[e + half] = from_f<T>(b * cs + a * sn);
+    } else if (d >= 2 * half) {
+      kc[e] = from_f<T>(k[e] * rk * wk[e]);
+    }
+  }
+  T* vc = vcache + crow * Nv;
+  for (int e = threadIdx.x; e < Nv; e += blockDim.x) vc[e] = from_f<T>(v[e]);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Sliding-window attention with grouped keys / values, mixed heads and a sink.  A tile is up to QT consecutive tokens of ONE
+// request with all H query heads (the mix needs every head's score of a (token, key) pair in one place).
+//   raw[h][j] = q_h . k_{h / (H / G)}[j]                            fp32
+//   s[h][j]   = sum_g mix[h][g] * raw[g][j]                         mix = talk[h][g] * temp[g] * scale, folded at load
+//   token at position p sees keys j with 0 <= p - j < window
+//   p[h][j]   = exp(s[h][j]) / (exp(sink[h]) + sum_j' exp(s[h][j']))  online over key tiles of KT keys, state (m, l) starts at (sink, 1)
+//   out[h]    = sum_j p[h][j] v_{h / (H / G)}[j]
+// nsplit > 1 (grid.y): the tile's key tiles are dealt over the splits, which leave (m, l, unnormalised sums) per (token, head)
+// row for latent_attn_merge_kernel; the sink enters in split 0 only.
+// ---------------------------------------------------------------------------------------------------------------------------
+struct WindowAttnParams {
+  const float* q;           // [tokens][ldq], the H * dim query values first
+  long long ldq;
+  const void* kcache;       // T [slots][cap][G * dim]
+  const void* vcache;       // T [slots][cap][G * vdim]
+  const float* mix;         // [H][H]
+  const float* sink;        // [H]
+  const int* tile_row0;     // first (token, head) row of the tile = first token * H
+  const int* tile_rows;     // rows of the tile = tokens * H
+  const int* tile_slot;
+  const int* tok_pos;
+  void* out;                // T [tokens][H * vdim]
+  float* part;              // nsplit > 1: [tile][split][QT * H][vdim + 2]
+  int cap, H, G, dim, vdim, window, QT, KT, nsplit, kstride;      // kstride: elements between staged key rows (odd number of words)
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) window_attn_kernel(WindowAttnParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int H = p.H, G = p.G, dim = p.dim, vdim = p.vdim, QT = p.QT, KT = p.KT, rep = H / G;
+  const int Nq = H * dim, Nk = G * dim, Nv = G * vdim, KS = KT + 1;
+  float* qs = reinterpret_cast<float*>(smem_raw);                  // [QT][Nq]
+  float* oacc = qs + QT * Nq;                                      // [QT][H * vdim]
+  float* sraw = oacc + QT * H * vdim;                              // [QT * H][KS]
+  float* sp = sraw + QT * H * KS;                                  // [QT * H][KS] mixed scores, then weights
+  float* mixs = sp + QT * H * KS;                                  // [H][H]
+  float* rm = mixs + H * H;                                        // [QT * H] running maximum
+  float* rl = rm + QT * H;                                         // [QT * H] running sum
+  float* rc = rl + QT * H;                                         // [QT * H] rescale factor of the current key tile
+  T* ks = reinterpret_cast<T*>(rc + QT * H);                       // [KT][kstride]
+  T* vs = ks + (size_t)KT * p.kstride;                             // [KT][Nv]
+  const int tile = blockIdx.x, split = blockIdx.y;
+  const int tok0 = p.tile_row0[tile] / H, nt = p.tile_rows[tile] / H;
+  const int p0 = p.tok_pos[tok0];                                  // positions p0 .. p0 + nt - 1
+  const T* kc = static_cast<const T*>(p.kcache) + (long long)p.tile_slot[tile] * p.cap * Nk;
+  const T* vc = static_cast<const T*>(p.vcache) + (long long)p.tile_slot[tile] * p.cap * Nv;
+  const int kmin = max(0, p0 - p.window + 1), kmax = p0 + nt - 1;
+  const int n_kt = (kmax - kmin) / KT + 1;
+  const int per = (n_kt + p.nsplit - 1) / p.nsplit;
+  const int kt0 = split * per, kt1 = min(n_kt, kt0 + per);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  for (int i = threadIdx.x; i < QT * Nq; i += 256) {
+    const int qt = i / Nq;
+    qs[i] = qt < nt ? p.q[(long long)(tok0 + qt) * p.ldq + (i - qt * Nq)] : 0.f;
+  }
+  for (int i = threadIdx.x; i < QT * H * vdim; i += 256) oacc[i] = 0.f;
+  for (int i = threadIdx.x; i < H * H; i += 256) mixs[i] = p.mix[i];
+  for (int i = threadIdx.x; i < QT * H; i += 256) {
+    if (split == 0) { rm[i] = p.sink[i % H]; rl[i] = 1.f; }        // the sink: one unit of weight at logit sink[h], no value
+    else { rm[i] = -INFINITY; rl[i] = 0.f; }
+  }
+
+  for (int kt = kt0; kt < kt1; ++kt) {
+    const int kb = kmin + kt * KT;
+    const int nk = min(KT, kmax + 1 - kb);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nk * Nk; i += 256) { const int j = i / Nk, e = i - j * Nk; ks[j * p.kstride + e] = kc[(long long)(kb + j) * Nk + e]; }
+    for (int i = threadIdx.x; i < nk * Nv; i += 256) vs[i] = vc[(long long)kb * Nv + i];
+    __syncthreads();
+    // raw scores: item (row = qt * H + h, key j), keys fastest
+    for (int i = threadIdx.x; i < QT * H * KT; i += 256) {
+      const int row = i / KT, j = i - row * KT;
+      float acc = 0.f;
+      if (j < nk && row / H < nt) {
+        const float* qv = qs + (row / H) * Nq + (row % H) * dim;
+        const T* kv = ks + j * p.kstride + ((row % H) / rep) * dim;
+        for (int d = 0; d < dim; ++d) acc = fmaf(qv[d], to_f(kv[d]), acc);
+      }
+      sraw[row * KS + j] = acc;
+    }
+    __syncthreads();
+    // mix over heads, mask, online softmax: one warp per row, lanes over keys
+    for (int row = warp; row < QT * H; row += 8) {
+      const int qt = row / H, h = row - qt * H;
+      const int pos = p0 + qt;
+      float mx = -INFINITY;
+      for (int j = lane; j < KT; j += 32) {
+        float s = -INFINITY;
+        const int kj = kb + j;
+        if (j < nk && qt < nt && kj <= pos && pos - kj < p.window) {
+          s = 0.f;
+          for (int g = 0; g < H; ++g) s = fmaf(mixs[h * H + g], sraw[(qt * H + g) * KS + j], s);
+        }
+        sp[row * KS + j] = s;
+        mx = fmaxf(mx, s);
+      }
+      mx = warp_max(mx);
+      const float mo = rm[row], mn = fmaxf(mo, mx);
+      float sum = 0.f;
+      for (int j = lane; j < KT; j += 32) {
+        const float s = sp[row * KS + j];
+        const float w = s > -INFINITY ? expf(s - mn) : 0.f;
+        sp[row * KS + j] = w;
+        sum += w;
+      }
+      sum = warp_sum(sum);
+      if (lane == 0) {
+        const float corr = mn > -INFINITY ? expf(mo - mn) : 1.f;  // mo = -inf, mn finite -> 0; both -inf: nothing seen yet
+        rc[row] = corr;
+        rl[row] = rl[row] * corr + sum;
+        rm[row] = mn;
+      }
+    }
+    __syncthreads();
+    // weighted sum of the values: item (row, c), c fastest
+    for (int i = threadIdx.x; i < QT * H * vdim; i += 256) {
+      const int row = i / vdim, c = i - row * vdim;
+      const T* vv = vs + ((row % H) / rep) * vdim + c;
+      const float* w = sp + row * KS;
+      float acc = oacc[i] * rc[row];
+      for (int j = 0; j < nk; ++j) acc = fmaf(w[j], to_f(vv[j * Nv]), acc);
+      oacc[i] = acc;
+    }
+  }
+  __syncthreads();
+  if (p.nsplit == 1) {
+    T* out = static_cast<T*>(p.out);
+    for (int i = threadIdx.x; i < nt * H * vdim; i += 256) out[(long long)tok0 * H * vdim + i] = from_f<T>(oacc[i] / rl[i / vdim]);
+  } else {
+    float* dst = p.part + ((long long)tile * p.nsplit + split) * (QT * H) * (vdim + 2);
+    for (int i = threadIdx.x; i < nt * H * vdim; i += 256) { const int row = i / vdim; dst[(long long)row * (vdim + 2) + (i - row * vdim)] = oacc[i]; }
+    for (int row = threadIdx.x; row < nt * H; row += 256) { dst[(long long)row * (vdim + 2) + vdim] = rm[row]; dst[(long long)row * (vdim + 2) + vdim + 1] = rl[row]; }
+  }
+}
+
+// fp32 rows -> T (the merged splits of the window attention)
+template <typename T>
+__global__ void rows_from_f32_kernel(const float* __restrict__ in, T* __restrict__ out, long long n) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i < n) out[i] = from_f<T>(in[i]);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Small projections whose result must be fp32 (gates of a recurrence, router logits): out[t][n] = x[t] . w[n] + b[n], one CTA
+// per token, the row in shared memory, one warp per output.  The sum over k has a fixed order whatever else is in the step.
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) small_proj_f32_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ w, const float* __restrict__ b,
+                                                             float* __restrict__ out, int N, int K) {
+  extern __shared__ float xrow[];
+  const long long t = blockIdx.x;
+  for (int i = threadIdx.x; i < K; i += blockDim.x) xrow[i] = to_f(x[t * ldx + i]);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int n = warp; n < N; n += 8) {
+    const T* wr = w + (long long)n * K;
+    float acc = 0.f;
+    for (int k = lane; k < K; k += 32) acc = fmaf(xrow[k], to_f(wr[k]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) out[t * N + n] = acc + (b ? b[n] : 0.f);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Recurrent matrix memories.  Per (request, head): S [dim][vdim] fp32, carried between steps (stored column-major,
+// St[slot][head][vdim][dim], so that a thread's rows of a column are contiguous); a sequence starts from zero (position 0).
+//   MODE_DECAY (gated linear attention): S <- diag(a_t) S + k_t v_t^T,  o_t = S^T q_t,   a_t = sigmoid(z_t + bz)^(1 / tau)
+//   MODE_EXPGATE (stabilised exponential gating, the matrix memory of xLSTM):
+//       i_t = cap tanh(gi / cap), f_t = logsigmoid(cap tanh(gf / cap)),  m_t = max(f_t + m_{t-1}, i_t)   (m starts at 0)
+//       S <- e^(f_t + m_{t-1} - m_t) S + e^(i_t - m_t) k_t v_t^T,  n likewise with k_t alone
+//       o_t = S^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6)
+// q is scaled by qscale.  A CTA owns 16 columns of one (request, head) and walks the request's new tokens in order; lane & 7
+// selects a group of rows (row = group + 8 i), so a column's dot product with q closes with three shuffles.  Tokens are staged
+// in shared memory TT at a time.  Grid: (entries * heads, ceil(vdim / 16)).
+// ---------------------------------------------------------------------------------------------------------------------------
+enum { MODE_DECAY = 0, MODE_EXPGATE = 1 };
+
+struct ScanParams {
+  const void* proj;         // T [tokens][ld]: q at off_q, k at off_k, v at off_v (heads x dim / vdim each)
+  long long ld;
+  int off_q, off_k, off_v;
+  const float* z;           // MODE_DECAY: [tokens][heads * dim] decay logits;  MODE_EXPGATE: [tokens][2 * heads] gate inputs (i then f, biased)
+  const float* zb;          // MODE_DECAY: bias [heads * dim]
+  float inv_tau, cap, qscale;
+  float* St;                // [slots][heads][vdim][dim]
+  float* nvec;              // MODE_EXPGATE: [slots][heads][column slices][dim]: every CTA of a head carries its own copy of n and m,
+  float* mval;              // MODE_EXPGATE: [slots][heads][column slices]        so that none reads what another has already replaced
+  const int* ent_tok0;      // per entry: first token of the step, number of tokens, slot, position of the first token
+  const int* ent_ntok;
+  const int* ent_slot;
+  const int* ent_pos0;
+  float* out;               // [tokens][heads * vdim]
+  int heads, dim, vdim;
+};
+
+template <typename T, int MODE, int R>      // R rows per thread: dim <= 8 * R
+__global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
+  constexpr int TT = 8;
+  extern __shared__ float sm[];
+  const int dim = p.dim, vdim = p.vdim, heads = p.heads;
+  float* ksm = sm;                      // [TT][dim]
+  float* qsm = ksm + TT * dim;          // [TT][dim]
+  float* asm_ = qsm + TT * dim;         // [TT][dim] decay factors (MODE_DECAY)
+  float* vsm = asm_ + TT * dim;         // [TT][16]
+  float* gsm = vsm + TT * 16;           // [TT][2] gate inputs (MODE_EXPGATE)
+  const int ent = blockIdx.x / heads, head = blockIdx.x - ent * heads;
+  const int tok0 = p.ent_tok0[ent], nt = p.ent_ntok[ent], slot = p.ent_slot[ent], pos0 = p.ent_pos0[ent];
+  const int rg = threadIdx.x & 7, cl = threadIdx.x >> 3, col = blockIdx.y * 16 + cl;
+  const bool col_ok = col < vdim;
+  float* Scol = p.St + (((long long)slot * heads + head) * vdim + (col_ok ? col : 0)) * dim;
+  const long long slice = ((long long)slot * heads + head) * gridDim.y + blockIdx.y;
+  float* nst = MODE == MODE_EXPGATE ? p.nvec + slice * dim : nullptr;
+  float S[R], nv[R], m = 0.f;
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    const int r = rg + 8 * i;
+    const bool live = pos0 > 0 && r < dim;
+    S[i] = live && col_ok ? Scol[r] : 0.f;
+    nv[i] = (MODE == MODE_EXPGATE && live) ? nst[r] : 0.f;
+  }
+  if (MODE == MODE_EXPGATE && pos0 > 0) m = p.mval[slice];
+  const T* proj = static_cast<const T*>(p.proj);
+
+  for (int t0 = 0; t0 < nt; t0 += TT) {
+    const int tn = min(TT, nt - t0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < tn * dim; i += 128) {
+      const int tt = i / dim, d = i - tt * dim;
+      const long long row = (long long)(tok0 + t0 + tt);
+      ksm[i] = to_f(proj[row * p.ld + p.off_k + head * dim + d]);
+      qsm[i] = to_f(proj[row * p.ld + p.off_q + head * dim + d]) * p.qscale;
+      if (MODE == MODE_DECAY) asm_[i] = expf(log_sigmoidf(p.z[row * heads * dim + head * dim + d] + p.zb[head * dim + d]) * p.inv_tau);
+    }
+    for (int i = threadIdx.x; i < tn * 16; i += 128) {
+      const int tt = i >> 4, c = blockIdx.y * 16 + (i & 15);
+      vsm[i] = c < vdim ? to_f(proj[(long long)(tok0 + t0 + tt) * p.ld + p.off_v + head * vdim + c]) : 0.f;
+    }
+    if (MODE == MODE_EXPGATE && threadIdx.x < tn * 2) {
+      const int tt = threadIdx.x >> 1, which = threadIdx.x & 1;
+      gsm[threadIdx.x] = p.z[(long long)(tok0 + t0 + tt) * 2 * heads + which * heads + head];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < tn; ++tt) {
+      const float v = vsm[tt * 16 + cl];
+      const float* kk = ksm + tt * dim;
+      const float* qq = qsm + tt * dim;
+      float acc = 0.f, nq = 0.f, fa = 1.f, fb = 1.f, m2 = 0.f;
+      if (MODE == MODE_EXPGATE) {
+        const float il = p.cap * tanhf(gsm[2 * tt] / p.cap);
+        const float fl = log_sigmoidf(p.cap * tanhf(gsm[2 * tt + 1] / p.cap));
+        m2 = fmaxf(fl + m, il);
+        fa = expf(fl + m - m2);
+        fb = expf(il - m2);
+        m = m2;
+      }
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const int r = rg + 8 * i;
+        if (r < dim) {
+          const float kv = kk[r], qv = qq[r];
+          if (MODE == MODE_DECAY) {
+            S[i] = fmaf(asm_[tt * dim + r], S[i], kv * v);
+          } else {
+            S[i] = fmaf(fa, S[i], fb * kv * v);
+            nv[i] = fmaf(fa, nv[i], fb * kv);
+            nq = fmaf(nv[i], qv, nq);
+          }
+          acc = fmaf(S[i], qv, acc);
+        }
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      if (MODE == MODE_EXPGATE) {
+        nq += __shfl_xor_sync(0xffffffffu, nq, 1);
+        nq += __shfl_xor_sync(0xffffffffu, nq, 2);
+        nq += __shfl_xor_sync(0xffffffffu, nq, 4);
+        acc = acc / (fmaxf(fabsf(nq), expf(-m2)) + 1e-6f);
+      }
+      if (rg == 0 && col_ok) p.out[(long long)(tok0 + t0 + tt) * heads * vdim + head * vdim + col] = acc;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    const int r = rg + 8 * i;
+    if (r < dim) {
+      if (col_ok) Scol[r] = S[i];
+      if (MODE == MODE_EXPGATE && cl == 0) nst[r] = nv[i];
+    }
+  }
+  if (MODE == MODE_EXPGATE && threadIdx.x == 0) p.mval[slice] = m;
+}
+
+// what leaves a recurrent mixer: per head rms_norm over vdim (weight w[h * wstride + c]: wstride = 0 shares one row between
+// the heads), times a gate computed from the projection g (act 0: sigmoid, 1: silu) -> T.  One warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, int wstride,
+                                                             const T* __restrict__ proj, long long ld, int off_g, int act, T* __restrict__ out,
+                                                             int heads, int vdim, long long rows, float eps) {
+  const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = row / heads; const int h = (int)(row - t * heads);
+  const float* src = o + row * vdim;
+  float s = 0.f;
+  for (int c = lane; c < vdim; c += 32) s += src[c] * src[c];
+  const float r = 1.f / sqrtf(warp_sum(s) / (float)vdim + eps);
+  for (int c = lane; c < vdim; c += 32) {
+    const float g = to_f(proj[t * ld + off_g + h * vdim + c]);
+    out[row * vdim + c] = from_f<T>(src[c] * r * w[(long long)h * wstride + c] * (act ? siluf(g) : sigmoidf(g)));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// End of a sublayer in the sandwich arrangement, one CTA per token:
+//   y = branch0                                                 (one mixer)
+//     | factor * (rms_norm(branch0) * w0 + rms_norm(branch1) * w1)   (two mixers side by side, each normed over the width)
+//     | sum_k ew[t][k] * branch0[t * top + k]                   (routed experts: weighted sum of the chosen experts' rows)
+//   x <- x + rms_norm(y) * w_post;  optional copy of x (per-layer trace);  optional h = rms_norm(x) * w_next as fp32 and / or T
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) sublayer_end_kernel(float* __restrict__ xin, const T* __restrict__ b0, const float* __restrict__ w0,
+                                                           const T* __restrict__ b1, const float* __restrict__ w1, float factor,
+                                                           const float* __restrict__ ew, int top, const float* __restrict__ w_post,
+                                                           float* __restrict__ trace, const float* __restrict__ w_next,
+                                                           float* __restrict__ h32, T* __restrict__ hT, int W, float eps) {
+  extern __shared__ float y[];
+  __shared__ float red[32];
+  const long long t = blockIdx.x;
+  float* x = xin + t * W;
+  if (ew) {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      float acc = 0.f;
+      for (int k = 0; k < top; ++k) acc = fmaf(ew[t * top + k], to_f(b0[(t * top + k) * W + i]), acc);
+      y[i] = acc;
+    }
+  } else if (b1) {
+    float s0 = 0.f, s1 = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) { const float a = to_f(b0[t * W + i]), b = to_f(b1[t * W + i]); s0 += a * a; s1 += b * b; }
+    const float r0 = 1.f / sqrtf(block_sum(s0, red) / (float)W + eps);
+    const float r1 = 1.f / sqrtf(block_sum(s1, red) / (float)W + eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) y[i] = factor * (to_f(b0[t * W + i]) * r0 * w0[i] + to_f(b1[t * W + i]) * r1 * w1[i]);
+  } else {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) y[i] = to_f(b0[t * W + i]);
+  }
+  __syncthreads();
+  const float ry = block_rrms(y, W, eps, red);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = x[i] + y[i] * ry * w_post[i];
+    x[i] = v;
+    y[i] = v;
+    if (trace) trace[t * W + i] = v;
+  }
+  if (w_next) {
+    __syncthreads();
+    const float rx = block_rrms(y, W, eps, red);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      const float v = y[i] * rx * w_next[i];
+      if (h32) h32[t * W + i] = v;
+      if (hT) hT[t * W + i] = from_f<T>(v);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Routed experts.  moe_route_kernel: per token (one warp) the `top` largest router logits (ties: the lower index) and the
+// softmax over those alone.  moe_group_kernel (ONE CTA): sorts the (token, choice) pairs by expert: pos-th row of the grouped
+// order is pair perm[pos] of token row_tok[pos], and cuts every expert's rows into tiles of 64 for the grouped products
+// (tile -> expert, first row, rows); n_tiles[0] = number of tiles.  The order inside an expert follows the atomics and may
+// differ from run to run; a row's result does not depend on it (every row of a product is summed on its own).
+// ---------------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, int E, int top, int* __restrict__ idx,
+                                                        float* __restrict__ wts, int n_tok) {
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= n_tok) return;
+  const float* z = logits + (long long)t * E;
+  float zmax = 0.f, den = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY; int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      bool taken = false;
+      for (int j = 0; j < k; ++j) taken |= idx[(long long)t * top + j] == e;
+      const float v = z[e];
+      if (!taken && (v > best || (v == best && e < bi))) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (k == 0) zmax = best;
+    const float w = expf(best - zmax);
+    den += w;
+    if (lane == 0) { idx[(long long)t * top + k] = bi; wts[(long long)t * top + k] = w; }
+    __syncwarp();
+  }
+  __syncwarp();
+  if (lane < top) wts[(long long)t * top + lane] /= den;
+}
+
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__ idx, int n_pairs, int top, int E, int* __restrict__ rank,
+                                                         int* __restrict__ perm, int* __restrict__ row_tok, int* __restrict__ tile_expert,
+                                                         int* __restrict__ tile_row0, int* __restrict__ tile_rows, int* __restrict__ n_tiles) {
+  extern __shared__ int cnt[];          // [E] counts, then [E] offsets
+  int* off = cnt + E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) rank[i] = atomicAdd(&cnt[idx[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, nt = 0;
+    for (int e = 0; e < E; ++e) {
+      off[e] = o;
+      for (int r0 = 0; r0 < cnt[e]; r0 += 64) { tile_expert[nt] = e; tile_row0[nt] = o + r0; tile_rows[nt] = min(64, cnt[e] - r0); ++nt; }
+      o += cnt[e];
+    }
+    n_tiles[0] = nt;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int pos = off[idx[i]] + rank[i];
+    perm[pos] = i;
+    row_tok[pos] = i / top;
+  }
+}
+
+// Grouped product of the routed experts: for tile (expert e, rows pos0 .. pos0 + n - 1 of the grouped order)
+//   C[c_rows ? c_rows[pos] : pos][:] = act( A[a_rows ? a_rows[pos] : pos][:] . B[e]^T ),  B[e] = B + e * sb, [N][K];  act 1: relu(.)^2
+// CUDA cores, fp32 FMA, k in order (the all-fp32 mode, and shapes the tensor-core kernel does not take).
+template <typename TA, typename TB, typename TC>
+__global__ void __launch_bounds__(256) grouped_gemm_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__ a_rows,
+                                                           const TB* __restrict__ B, long long ldb, long long sb, TC* __restrict__ C,
+                                                           long long ldc, const int* __restrict__ c_rows, const int* __restrict__ tile_expert,
+                                                           const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
+                                                           const int* __restrict__ n_tiles, int N, int K, int act) {
+  constexpr int BM = 64, BN = 64, BK = 16;
+  if ((int)blockIdx.y >= n_tiles[0]) return;
+  __shared__ float As[BK][BM + 1], Bs[BK][BN + 1];
+  __shared__ int arow[BM];
+  const int pos0 = tile_row0[blockIdx.y], M = tile_rows[blockIdx.y];
+  B += (long long)tile_expert[blockIdx.y] * sb;
+  const int n0 = blockIdx.x * BN;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  if (threadIdx.x < BM) arow[threadIdx.x] = threadIdx.x < M ? (a_rows ? a_rows[pos0 + threadIdx.x] : pos0 + threadIdx.x) : 0;
+  __syncthreads();
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int rr = ty + 16 * i, kk = k0 + tx;
+      As[tx][rr] = (rr < M && kk < K) ? to_f(A[(long long)arow[rr] * lda + kk]) : 0.f;
+      Bs[tx][rr] = (n0 + rr < N && kk < K) ? to_f(B[(long long)(n0 + rr) * ldb + kk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { a[i] = As[k][ty + 16 * i]; b[i] = Bs[k][tx + 16 * i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int m = ty + 16 * i, n = n0 + tx + 16 * j;
+      if (m < M && n < N) {
+        float v = acc[i][j];
+        if (act) { v = fmaxf(v, 0.f); v = v * v; }
+        const long long crow = c_rows ? c_rows[pos0 + m] : pos0 + m;
+        C[crow * ldc + n] = from_f<TC>(v);
+      }
+    }
+}
+
+// The same grouped product on the tensor cores (mma.sync m16n8k16, bf16 in, fp32 accumulate): K a multiple of 16, rows of A
+// and B on 16-byte boundaries.  CTA tile 64 x 64, 4 warps of 16 rows.
+__global__ void __launch_bounds__(128) grouped_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __restrict__ a_rows,
+                                                               const bf16* __restrict__ B, long long ldb, long long sb, bf16* __restrict__ C,
+                                                               long long ldc, const int* __restrict__ c_rows, const int* __restrict__ tile_expert,
+                                                               const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
+                                                               const int* __restrict__ n_tiles, int N, int K, int act) {
+  constexpr int BM = 64, BN = 64, BK = 32, ST = BK + 8;
+  if ((int)blockIdx.y >= n_tiles[0]) return;
+  __shared__ __align__(16) bf16 As[BM][ST];
+  __shared__ __align__(16) bf16 Bs[BN][ST];
+  __shared__ int arow[BM];
+  const int pos0 = tile_row0[blockIdx.y], M = tile_rows[blockIdx.y];
+  B += (long long)tile_expert[blockIdx.y] * sb;
+  const int n0 = blockIdx.x * BN;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+  if (threadIdx.x < BM) arow[threadIdx.x] = threadIdx.x < M ? (a_rows ? a_rows[pos0 + threadIdx.x] : pos0 + threadIdx.x) : 0;
+  __syncthreads();
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+  uint4 ra[2], rb[2];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int c = threadIdx.x + 128 * j;
+      const int rr = c / 4, kk = (c % 4) * 8;
+      ra[j] = (rr < M && k0 + kk < K) ? *reinterpret_cast<const uint4*>(A + (long long)arow[rr] * lda + k0 + kk) : make_uint4(0u, 0u, 0u, 0u);
+      rb[j] = (n0 + rr < N && k0 + kk < K) ? *reinterpret_cast<const uint4*>(B + (long long)(n0 + rr) * ldb + k0 + kk) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  fetch(0);
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int c = threadIdx.x + 128 * j;
+      *reinterpret_cast<uint4*>(&As[c / 4][(c % 4) * 8]) = ra[j];
+      *reinterpret_cast<uint4*>(&Bs[c / 4][(c % 4) * 8]) = rb[j];
+    }
+    __syncthreads();
+    if (k0 + BK < K) fetch(k0 + BK);
+#pragma unroll
+    for (int ks = 0; ks < BK / 16; ++ks) {
+      unsigned a[4];
+      const int mi = lane >> 3;
+      ldmatrix_x4(a, &As[warp * 16 + (mi & 1) * 8 + (lane & 7)][ks * 16 + (mi >> 1) * 8]);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        unsigned b[4];
+        ldmatrix_x4(b, &Bs[np * 16 + (mi >> 1) * 8 + (lane & 7)][ks * 16 + (mi & 1) * 8]);
+        mma_bf16_16816(acc[2 * np], a, b[0], b[1]);
+        mma_bf16_16816(acc[2 * np + 1], a, b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int m = warp * 16 + g + 8 * hf, n = n0 + nb * 8 + 2 * t4;
+      if (m < M) {
+        const long long crow = c_rows ? c_rows[pos0 + m] : pos0 + m;
+        float v0 = acc[nb][2 * hf], v1 = acc[nb][2 * hf + 1];
+        if (act) { v0 = fmaxf(v0, 0.f); v0 *= v0; v1 = fmaxf(v1, 0.f); v1 *= v1; }
+        if (n < N) C[crow * ldc + n] = __float2bfloat16_rn(v0);
+        if (n + 1 < N) C[crow * ldc + n + 1] = __float2bfloat16_rn(v1);
+      }
+    }
+}
+
+// logits <- cap * tanh(logits / cap) on fp32 rows; `in` may be the padded bf16 rows of the tensor-core head (ld elements per row)
+__global__ void softcap_rows_kernel(const bf16* __restrict__ in_bf, long long ld, float* __restrict__ out, int V, long long n, float cap) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n) return;
+  const long long row = i / V;
+  const float v = in_bf ? __bfloat162float(in_bf[row * ld + (i - row * V)]) : out[i];
+  out[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+}
+
+}  // namespace dlm
+}  // namespace b200

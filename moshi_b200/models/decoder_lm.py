@@ -12,9 +12,17 @@ import typing as tp
 import torch
 
 from .. import _lib
-from ..config import MIXERS, MLP_KINDS, DecoderLMConfig
+from ..config import BLOCKS, MIXERS, MLP_KINDS, DecoderLMConfig, MixerConfig
 
 _DTYPES = {torch.bfloat16: _lib.B200_BF16, torch.float32: _lib.B200_F32}
+
+
+def _fill_mixer(dst, m: MixerConfig) -> None:
+    dst.kind, dst.heads, dst.dim, dst.vdim, dst.kv_heads, dst.kv_rank = MIXERS[m.kind], m.heads, m.dim, m.vdim, m.kv_heads, m.kv_rank
+    dst.scale, dst.window, dst.conv_taps, dst.rot_dims, dst.rot_base = m.scale, m.window, m.conv, m.rot_dims, m.rot_base
+    sc = m.rot_scaling or {}
+    dst.rot_factor, dst.rot_low, dst.rot_high = float(sc.get("factor", 0.0)), float(sc.get("low", 1.0)), float(sc.get("high", 1.0))
+    dst.rot_original, dst.gate_cap, dst.tau = float(sc.get("original", 0.0)), m.gate_cap, m.tau
 
 
 class DecoderLM:
@@ -36,11 +44,15 @@ class DecoderLM:
         self._h = C.c_void_p()
         layers = (_lib.DLMLayerC * len(cfg.layers))()
         for i, L in enumerate(cfg.layers):
-            layers[i].mixer, layers[i].heads, layers[i].dim, layers[i].vdim = MIXERS[L.type], L.heads, L.dim, L.vdim
-            layers[i].kv_rank, layers[i].scale, layers[i].mlp, layers[i].ff = L.kv_rank, L.scale, MLP_KINDS[L.mlp_kind], L.ff
+            layers[i].mixer, layers[i].mlp, layers[i].ff = MIXERS[L.type], MLP_KINDS[L.mlp_kind], L.ff
+            layers[i].experts, layers[i].top = L.experts, L.top
+            for dst, m in zip((layers[i].a, layers[i].b), L.mixers()):
+                if m is not None:
+                    _fill_mixer(dst, m)
         c = _lib.DLMConfigC()
         c.vocab, c.width, c.n_layers = cfg.vocab, cfg.width, len(cfg.layers)
         c.embedding_scale, c.residual_mult, c.norm_eps = cfg.embedding_scale, cfg.residual_mult, cfg.norm_eps
+        c.block, c.canon_taps, c.logit_softcap = BLOCKS[cfg.block], cfg.canon_taps, cfg.logit_softcap
         c.compute_dtype = _DTYPES[dtype]
         c.layers = layers
         items = tensors.items() if isinstance(tensors, tp.Mapping) else tensors
@@ -117,9 +129,9 @@ class DecoderLMGen:
 
     def kernel_times(self, reset: bool = True) -> dict[str, float]:
         """Milliseconds per class of operation since the last reset (needs ``set_option("time_kernels", 1)``)."""
-        ms = (C.c_double * 4)()
+        ms = (C.c_double * 6)()
         _lib.check(self._lib.b200_dlm_read_timers(self._h, ms, int(reset)))
-        return dict(zip(("linear", "attention", "fold", "elementwise"), (float(x) for x in ms)))
+        return dict(zip(("linear", "attention", "fold", "elementwise", "recurrent", "experts"), (float(x) for x in ms)))
 
     def release(self, slot: int) -> None:
         """The slot's request is finished: what it holds is given back."""

@@ -277,9 +277,18 @@ def iter_synth_decoder_tensors(cfg: DecoderLMConfig, seed: int = 99, device="cpu
     gen = _gen(seed, device)
     for name, shape in cfg.tensor_shapes().items():
         leaf = name.split(".", 1)[-1] if name.startswith("l") and name[1].isdigit() else name
-        if leaf in ("norm1", "final.norm", "mix.dkv.norm"):
+        last = leaf.rsplit(".", 1)[-1]
+        if leaf in ("norm1", "final.norm", "mix.dkv.norm") or (len(shape) == 1 and last in ("norm", "norm1b", "norm2", "norm2b", "out")):
             t = 1.0 + _uniform(gen, shape, 0.2, device)
-        elif leaf.endswith(".b") or leaf == "mix.sink":
+        elif last == "temp":
+            t = 1.0 + _uniform(gen, shape, 0.3, device)
+        elif last == "talk":          # near the identity: every head keeps most of its own score
+            t = torch.eye(shape[0], device=device) + _uniform(gen, shape, 0.5 / shape[0], device)
+        elif last == "conv" or leaf == "canon1":
+            t = _uniform(gen, shape, 0.5, device)
+        elif last == "b" and leaf.endswith(("a2.b", "f.b")):      # decays and forget gates start open: memories reach far back
+            t = 2.0 + _uniform(gen, shape, 1.0, device)
+        elif leaf.endswith(".b") or last == "sink":
             t = _uniform(gen, shape, 0.5, device)
         elif leaf == "dwa":
             t = torch.rand(shape, generator=gen, device=device) + 0.2
