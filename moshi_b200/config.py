@@ -469,7 +469,7 @@ class GovuvikConfig(DecoderLMConfig):
                 a, b, l, r = L.a, L.b, p + "mix.left.", p + "mix.right."
                 nq, nk, nv = a.heads * a.dim, a.kv_heads * a.dim, a.kv_heads * a.vdim
                 out.update({l + "q": (nq, W), l + "k": (nk, W), l + "v": (nv, W), l + "q.norm": (nq,), l + "k.norm": (nk,)})
-                if a.conv > 1:
+                if a.conv >= 1:
                     out.update({l + "q.conv": (nq, a.conv), l + "k.conv": (nk, a.conv), l + "v.conv": (nv, a.conv)})
                 out.update({l + "talk": (a.heads, a.heads), l + "temp": (a.heads,), l + "sink": (a.heads,), l + "o": (W, a.heads * a.vdim),
                             r + "q": (b.heads * b.dim, W), r + "k": (b.heads * b.dim, W), r + "v": (b.heads * b.vdim, W),

@@ -453,7 +453,7 @@ int finalize_sandwich_layer(b200_dlm* h, int i, std::vector<void*>& drop) {
     // left: window attention
     B200_TRY(get_f32(h, l + "q.norm", L.Nq, &L.qnorm));
     B200_TRY(get_f32(h, l + "k.norm", L.Nk, &L.knorm));
-    if (a.conv_taps > 1) {
+    if (a.conv_taps >= 1) {
       const int C = L.Nq + L.Nk + L.Nv, taps = a.conv_taps;
       B200_TRY(h->weights.alloc_t(&L.qkv_conv, (size_t)C * taps, false));
       const Tensor* t = nullptr;

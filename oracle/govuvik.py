@@ -143,7 +143,7 @@ class GovuvikOracle:
     @staticmethod
     def _push(history, u, keep):
         history.append(u)
-        if len(history) > keep:
+        while len(history) > keep:
             del history[0]
 
     def _parallel(self, i, m, h, pos, st):
@@ -153,8 +153,11 @@ class GovuvikOracle:
         proj = {}
         for name in ("q", "k", "v"):
             u = W[p + f"left.{name}"] @ h
-            proj[name] = causal_conv_step(st[name], u, W[p + f"left.{name}.conv"])
-            self._push(st[name], u, int(l["conv"]) - 1)
+            if int(l.get("conv", 0)) >= 1:
+                proj[name] = causal_conv_step(st[name], u, W[p + f"left.{name}.conv"])
+                self._push(st[name], u, int(l["conv"]) - 1)
+            else:
+                proj[name] = u
         q = rms_norm(proj["q"], W[p + "left.q.norm"], eps).view(H, dim)
         k = rms_norm(proj["k"], W[p + "left.k.norm"], eps).view(G, dim)
         q, k = rope_rotate(q, pos, self.freqs[i]), rope_rotate(k, pos, self.freqs[i])
