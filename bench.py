@@ -685,6 +685,107 @@ def decoder_lm_arm(args) -> None:
     print(json.dumps(out))
 
 
+# ---------------------------------------------------------------------------------------------
+# --decoder-lm --decoder-arch govuvik: the Govuvik design beside the Likosun decoder LM (the closest existing model: same handle,
+# same step, prompts and decoding) at equal width, depth and vocabulary
+# ---------------------------------------------------------------------------------------------
+GOVUVIK_SIZES = {
+    # name: (width, layers, attention heads, kv heads, head dim, window, recurrent heads, key dim, value dim, experts, top, expert ff, vocab)
+    "w2048": (2048, 4, 16, 4, 128, 1024, 8, 128, 256, 16, 2, 4096, 32000),
+    "w4096": (4096, 2, 32, 8, 128, 1024, 16, 128, 256, 16, 2, 8192, 32000),
+}
+
+
+def _govuvik_cfg(size: str):
+    from moshi_b200.config import DecoderLMConfig
+    W, L, H, G, d, win, Hr, dk, dv, E, top, ff, V = GOVUVIK_SIZES[size]
+    moe = {"expert": {"ff": ff}, "kind": "moe", "router": {"experts": E, "top": top}}
+    left = {"conv": 4, "dim": d, "heads": H, "kv_heads": G, "mask": {"size": win}, "scale": d ** -0.5, "vdim": d,
+            "rot": {"base": 500000.0, "dims": d // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    pair = {"type": "parallel", "mixer": {"left": left, "right": {"dim": dk, "heads": Hr, "tau": 16.0, "vdim": dv, "decay_rank": 32}}, "mlp": moe}
+    rec = {"type": "mlstm", "mixer": {"dim": dk, "gate_cap": 15.0, "heads": Hr, "vdim": dv}, "mlp": moe}
+    return DecoderLMConfig.from_dict({"architecture": "Govuvik", "canon": {"taps": 4}, "logit_softcap": 30.0, "norm": {"eps": 1e-6}, "vocab": V,
+                                      "width": W, "layers": [pair if i % 2 == 0 else rec for i in range(L)]})
+
+
+def govuvik_arm(args) -> None:
+    """Prefill (one prompt of --prefill-tokens) and decode (--decode-batch requests, one token each, on --context cached tokens)
+    of the Govuvik design with random weights, per size, whole steps and per class of kernel against the measured rooflines; the
+    Likosun numbers of the same width and depth come from `--decoder-lm` without `--decoder-arch`."""
+    from moshi_b200 import _lib
+    from moshi_b200.models import DecoderLMGen, loaders
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    hbm, src = _peaks()
+    pk = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    tf = float(pk.get("bf16_tflops", 1590.0))
+    T, B, ctx = args.prefill_tokens, args.decode_batch, args.context
+    g = torch.Generator().manual_seed(7)
+    out = {"impl": "b200", "mode": "decoder-lm", "arch": "govuvik", "dtype": "bf16", "data": "synthetic (random weights)",
+           "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src}, "workload": {"prefill_tokens": T, "decode_batch": B, "context": ctx}, "sizes": {}}
+    launches0 = _lib.lib().b200_launch_count()
+    for size in args.decoder_sizes.split(","):
+        cfg = _govuvik_cfg(size)
+        W, L, H, G, d, win, Hr, dk, dv, E, top, ff, V = GOVUVIK_SIZES[size]
+        n_pair, n_rec = (L + 1) // 2, L // 2
+        model = loaders.get_decoder_lm(None, cfg, device=device, synth_seed=11)
+        res = {"config": dict(zip(("width", "layers", "heads", "kv_heads", "head_dim", "window", "recurrent_heads", "key_dim", "value_dim", "experts", "top",
+                                   "expert_ff", "vocab"), GOVUVIK_SIZES[size]))}
+        gen = DecoderLMGen(model, slots=B, capacity=ctx + 64, max_step_tokens=max(T, B), max_want=B)
+        prompt = torch.randint(0, V, (T,), generator=g).tolist()
+
+        def prefill():
+            gen.step([(0, prompt)], [T - 1])
+            gen.release(0)
+        ms = _timed_steps(prefill, args.steps, args.warmup)
+        gen.set_option("time_kernels", 1)
+        gen.kernel_times()
+        for _ in range(3):
+            prefill()
+        kt = {k: v / 3 for k, v in gen.kernel_times().items()}
+        gen.set_option("time_kernels", 0)
+        fl = model.algorithmic_flops(T, 0)
+        pairs = sum(min(t + 1, win) for t in range(T))
+        attn_fl = 2 * pairs * H * 2 * d * n_pair
+        exp_fl = (4 * T * top * W * ff + 2 * T * W * E) * L
+        rec_fl = 4 * T * Hr * dk * dv * L
+        lin_fl = fl - attn_fl - exp_fl - rec_fl
+        res["prefill"] = {"ms": ms, "tokens_per_s": T / ms * 1e3, "tflops": fl / ms / 1e9, "frac_of_bf16_peak": fl / ms / 1e9 / tf, "kernel_ms": kt,
+                          "kernel_frac_of_bf16_peak": {"linear": lin_fl / kt["linear"] / 1e9 / tf, "attention": attn_fl / kt["attention"] / 1e9 / tf,
+                                                       "experts": exp_fl / kt["experts"] / 1e9 / tf, "recurrent": rec_fl / kt["recurrent"] / 1e9 / tf}}
+        filler = torch.randint(0, V, (ctx,), generator=g).tolist()
+        for b in range(B):
+            for a in range(0, ctx, max(T, B)):
+                gen.step([(b, filler[a:a + max(T, B)])], [])
+        toks = torch.randint(0, V, (B,), generator=g).tolist()
+
+        def decode():
+            gen.step([(b, [toks[b]]) for b in range(B)], list(range(B)))
+        n_dec = min(args.steps, 40)
+        ms = _timed_steps(decode, n_dec, min(args.warmup, 5))
+        gen.set_option("time_kernels", 1)
+        gen.kernel_times()
+        for _ in range(3):
+            decode()
+        kt = {k: v / 3 for k, v in gen.kernel_times().items()}
+        gen.set_option("time_kernels", 0)
+        nbytes = model.algorithmic_bytes(B, B * ctx)
+        attn_bytes = B * min(ctx, win) * 2 * G * d * 2 * n_pair
+        rec_bytes = 2 * B * Hr * dk * dv * 4 * L
+        exp_bytes = min(E, B * top) * 2 * ff * W * 2 * L
+        lin_bytes = nbytes - attn_bytes - rec_bytes - exp_bytes
+        res["decode"] = {"ms": ms, "tokens_per_s": B / ms * 1e3, "algorithmic_bytes": nbytes, "frac_of_hbm_peak": nbytes / ms / 1e6 / hbm, "kernel_ms": kt,
+                         "kernel_frac_of_hbm_peak": {"linear": lin_bytes / kt["linear"] / 1e6 / hbm, "attention": attn_bytes / kt["attention"] / 1e6 / hbm,
+                                                     "recurrent": rec_bytes / kt["recurrent"] / 1e6 / hbm, "experts": exp_bytes / kt["experts"] / 1e6 / hbm}}
+        assert gen.error_flags() == 0
+        gen.close()
+        del gen, model
+        torch.cuda.empty_cache()
+        out["sizes"][size] = res
+    out["gpu_launches"] = int(_lib.lib().b200_launch_count() - launches0)
+    print(json.dumps(out))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -702,13 +803,15 @@ def main() -> None:
     ap.add_argument("--decoder-lm", action="store_true",
                     help="instead of the default workload: prefill / decode throughput of the text-only decoder LM (Likosun design, random "
                          "weights) beside the Moshi temporal transformer at equal width and depth; prints its own JSON line")
+    ap.add_argument("--decoder-arch", choices=["likosun", "govuvik"], default="likosun",
+                    help="with --decoder-lm: which design to time (govuvik: window attention beside gated linear attention, mLSTM, routed experts)")
     ap.add_argument("--decoder-sizes", default="w2048,w4096", help="comma-separated names out of " + ",".join(DECODER_SIZES))
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--decode-batch", type=int, default=32)
     ap.add_argument("--context", type=int, default=2048)
     args = ap.parse_args()
     if args.decoder_lm:
-        decoder_lm_arm(args)
+        govuvik_arm(args) if args.decoder_arch == "govuvik" else decoder_lm_arm(args)
         return
     if args.impl == "reference":
         reference_arm(args)

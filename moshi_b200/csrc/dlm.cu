@@ -1199,20 +1199,51 @@ int b200_dlm_read_timers(b200_dlm* h, double* ms6_host, int reset) {
   return B200_OK;
 }
 
-// weights once + the cached latents the new tokens read + the latents they write
+// weights once + what the new tokens read of the cache and state + what they write.  `context` = cached tokens over all
+// requests of the step; the sandwich block also needs `tokens` = requests when decoding (one state per request), which is what
+// the caller passes there.  Routed experts: every expert's weights count once when the step has at least `experts` (token,
+// choice) pairs, else tokens * top experts.
 int64_t b200_dlm_algorithmic_bytes(b200_dlm* h, int tokens, int context) {
   if (!h) return 0;
-  int64_t b = h->weight_bytes - (int64_t)h->cfg.vocab * h->cfg.width * esize(h);     // the embedding is gathered, not streamed
-  for (auto& L : h->layers) b += ((int64_t)context + tokens) * L.c.a.kv_rank * esize(h);
-  return b + (int64_t)tokens * h->cfg.width * esize(h);
+  const int64_t es = esize(h), W = h->cfg.width;
+  int64_t b = h->weight_bytes - (int64_t)h->cfg.vocab * W * es;     // the embedding is gathered, not streamed
+  if (h->cfg.block != B200_BLOCK_SANDWICH) {
+    for (auto& L : h->layers) b += ((int64_t)context + tokens) * L.c.a.kv_rank * es;
+    return b + (int64_t)tokens * W * es;
+  }
+  for (auto& L : h->layers) {
+    const b200_dlm_mixer &a = L.c.a, &m = L.c.mixer == B200_MIXER_PARALLEL ? L.c.b : L.c.a;
+    if (L.c.mixer == B200_MIXER_PARALLEL) {
+      const int64_t seen = tokens > 0 ? std::min<int64_t>((int64_t)context / tokens, a.window) * tokens : 0;      // decoding: every request reads its window
+      b += (seen + tokens) * (L.Nk + L.Nv) * es;
+    }
+    b += 2 * (int64_t)tokens * m.heads * m.dim * m.vdim * 4;        // the matrix memories, read and written
+    if (L.c.mlp == B200_MLP_MOE_RELU2) {
+      const int64_t used = std::min<int64_t>(L.c.experts, (int64_t)tokens * L.c.top);
+      b -= (int64_t)(L.c.experts - used) * 2 * L.c.ff * W * es;
+    }
+  }
+  return b + (int64_t)tokens * W * es;
 }
 
-// multiply-adds x 2 of the linears and of attention in the form the kernels run it (scores and sums against the latent)
+// multiply-adds x 2 of the linears and of attention in the form the kernels run it (scores and sums against the latent; the
+// window attention over the keys a token sees; routed experts for the chosen ones only; the recurrences' update and read-out)
 int64_t b200_dlm_algorithmic_flops(b200_dlm* h, int tokens, int context) {
   if (!h) return 0;
   const int64_t T = tokens, W = h->cfg.width;
   int64_t f = 0;
   for (auto& L : h->layers) {
+    if (h->cfg.block == B200_BLOCK_SANDWICH) {
+      const b200_dlm_mixer &a = L.c.a, &m = L.c.mixer == B200_MIXER_PARALLEL ? L.c.b : L.c.a;
+      f += 2 * T * W * L.ncat + 2 * T * W * m.heads * m.vdim + 4 * T * m.heads * m.dim * m.vdim;
+      if (L.c.mixer == B200_MIXER_PARALLEL) {
+        int64_t pairs = 0;       // (query, key) pairs of one prompt of T tokens on top of `context`
+        for (int64_t t = 0; t < T; ++t) pairs += std::min<int64_t>(context + t + 1, a.window);
+        f += 2 * pairs * a.heads * (a.dim + a.vdim) + 2 * T * W * a.heads * a.vdim + 2 * T * L.decay_rank * m.heads * m.dim;
+      }
+      if (L.c.mlp == B200_MLP_MOE_RELU2) f += 4 * T * L.c.top * W * L.c.ff + 2 * T * W * L.c.experts;
+      continue;
+    }
     const int64_t H = L.c.a.heads, dk = L.c.a.dim, dv = L.c.a.vdim, r = L.c.a.kv_rank;
     f += 2 * T * W * L.ncat + 2 * T * H * dk * r + 2 * T * H * dv * r + 2 * T * W * H * dv;
     if (L.c.mlp != B200_MLP_NONE) f += 2 * T * W * L.c.ff;
