@@ -37,6 +37,7 @@ struct Layer {
   // window attention (a)
   int a_q = 0, a_k = 0, a_v = 0, a_g = 0;         // offsets into the concatenated projection
   int Nq = 0, Nk = 0, Nv = 0, QT = 0, KT = 0, kstride = 0; size_t attn_smem = 0;
+  int sig_mma = -1, mma_items = 0; size_t mma_smem = 0;      // tensor-core window attention: tile list of 16 tokens, items per warp
   float *qnorm = nullptr, *knorm = nullptr, *qkv_conv = nullptr, *qkv_hist = nullptr, *mixhh = nullptr; double* freq = nullptr;
   void *kcache = nullptr, *vcache = nullptr;
   Weight a_o;
@@ -91,8 +92,8 @@ struct b200_dlm {
   int last_tokens = 0, last_want = 0;
   int* err = nullptr;
   // sandwich block: step metadata per token (first / last token of its request in the step) and per entry, further buffers
-  int off_first = 0, off_last = 0, off_ent_tok0 = 0, off_ent_ntok = 0, off_ent_slot = 0, off_ent_pos0 = 0, n_entries = 0;
-  float *embw = nullptr, *h32 = nullptr, *qkv32 = nullptr, *scan32 = nullptr, *gate32 = nullptr, *attn32 = nullptr, *route32 = nullptr, *moe_w = nullptr;
+  int off_first = 0, off_last = 0, off_ent_tok0 = 0, off_ent_ntok = 0, off_ent_slot = 0, off_ent_pos0 = 0, n_entries = 0, max_entry_tokens = 0;
+  float *embw = nullptr, *h32 = nullptr, *qkv32 = nullptr, *scan32 = nullptr, *gate32 = nullptr, *attn32 = nullptr, *route32 = nullptr, *moe_w = nullptr, *scan_prep = nullptr, *scan_v = nullptr;
   void *mixo2 = nullptr, *obuf2 = nullptr, *yexp = nullptr;
   int *moe_idx = nullptr, *moe_rank = nullptr, *moe_perm = nullptr, *moe_row_tok = nullptr, *moe_tile_e = nullptr, *moe_tile_r0 = nullptr,
       *moe_tile_n = nullptr, *moe_ntiles = nullptr;
@@ -403,7 +404,7 @@ size_t window_attn_smem(const b200_dlm_mixer& m, int QT, int KT, size_t es, int*
   const size_t Nq = (size_t)m.heads * m.dim, Nk = (size_t)m.kv_heads * m.dim, Nv = (size_t)m.kv_heads * m.vdim, rows = (size_t)QT * m.heads;
   const size_t words = ((Nk * es + 3) / 4) | 1;           // an odd number of 32-bit words between staged key rows
   *kstride = (int)(words * 4 / es);
-  return 4 * (QT * Nq + rows * m.vdim + 2 * rows * (KT + 1) + (size_t)m.heads * m.heads + 3 * rows) + es * ((size_t)KT * *kstride + KT * Nv) + 16;
+  return 4 * (QT * Nq + rows * m.vdim + 2 * rows * (KT + 1) + (size_t)m.heads * m.heads + 3 * rows) + es * ((size_t)KT * *kstride + KT * Nv) + 32;
 }
 
 int add_sig(b200_dlm* h, int H, int rpt) {
@@ -494,6 +495,12 @@ int finalize_sandwich_layer(b200_dlm* h, int i, std::vector<void*>& drop) {
     }
     if (!L.QT) B200_FAIL(B200_ERR_SHAPE, "decoder LM: layer %d: the window attention's heads do not fit shared memory", i);
     L.sig = add_sig(h, a.heads, L.QT * a.heads);
+    if (!h->f32 && a.dim % 16 == 0 && a.vdim % 16 == 0) {     // bf16 cache, fragment-sized heads: the tensor-core kernel, if it fits
+      const size_t Hh = a.heads, QS = L.Nq + 8, KS = L.Nk + 8, VS = L.Nv + 8;
+      const size_t sm = 2 * (16 * QS + 32 * KS + 32 * VS + Hh * 16 * 40) + 4 * (Hh * 16 * 40 + Hh * Hh + 3 * Hh * 16);
+      const int items = ceil_div(a.heads * ceil_div(a.vdim, 64), 8);
+      if (sm <= 220 * 1024 && items <= 4) { L.sig_mma = add_sig(h, a.heads, 16 * a.heads); L.mma_items = items <= 2 ? items : 4; L.mma_smem = sm; }
+    }
     // right: gated linear attention
     B200_TRY(matrix(r + "a2", Rq, L.decay_rank, &L.a2));
     B200_TRY(get_f32(h, r + "a2.b", Rq, &L.a2b));
@@ -553,41 +560,72 @@ int small_proj(b200_dlm* h, const T* x, long long ldx, const void* w, const floa
   return check_launch("small_proj_f32");
 }
 
-template <typename T, int MODE>
-int launch_scan(cudaStream_t st, const ScanParams& p, int n_entries) {
+template <int MODE, int R>
+int launch_scan_r(cudaStream_t st, const ScanParams& p, int n_entries) {
   const dim3 grid(n_entries * p.heads, ceil_div(p.vdim, 16));
-  const size_t smem = (size_t)(3 * 8 * p.dim + 8 * 16 + 8 * 2) * 4;
-  if (p.dim <= 32) B200_LAUNCH((matrix_memory_scan_kernel<T, MODE, 4>), grid, 128, smem, st, p);
-  else if (p.dim <= 64) B200_LAUNCH((matrix_memory_scan_kernel<T, MODE, 8>), grid, 128, smem, st, p);
-  else if (p.dim <= 128) B200_LAUNCH((matrix_memory_scan_kernel<T, MODE, 16>), grid, 128, smem, st, p);
-  else B200_LAUNCH((matrix_memory_scan_kernel<T, MODE, 32>), grid, 128, smem, st, p);
+  const size_t smem = (size_t)2 * p.stage * (p.prow + 16) * 4;
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA(cudaFuncSetAttribute((matrix_memory_scan_kernel<MODE, R>), cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+    attr_set = true;
+  }
+  B200_LAUNCH((matrix_memory_scan_kernel<MODE, R>), grid, 128, smem, st, p);
   return check_launch("matrix_memory_scan");
+}
+
+// prep rows (q, k and the decay or the two gates, fp32) for every token of the step, then the recurrence per (request, head)
+template <typename T, int MODE>
+int launch_scan(b200_dlm* h, ScanParams p, int n_tok) {
+  p.prow = ((MODE == MODE_DECAY ? 3 : 2) * p.dim + (MODE == MODE_EXPGATE ? 2 : 0) + 3) / 4 * 4;
+  p.prep = h->scan_prep; p.vprep = h->scan_v;
+  p.vec = p.vdim % 4 == 0;
+  p.stage = h->max_entry_tokens <= 8 ? 8 : 16;
+  B200_LAUNCH((scan_prep_kernel<T, MODE>), n_tok, 256, 0, h->stream, p);
+  B200_TRY(check_launch("scan_prep"));
+  if (p.dim <= 32) return launch_scan_r<MODE, 4>(h->stream, p, h->n_entries);
+  if (p.dim <= 64) return launch_scan_r<MODE, 8>(h->stream, p, h->n_entries);
+  if (p.dim <= 128) return launch_scan_r<MODE, 16>(h->stream, p, h->n_entries);
+  return launch_scan_r<MODE, 32>(h->stream, p, h->n_entries);
 }
 
 template <typename T>
 int window_attention(b200_dlm* h, const Layer& L, int n_tok, int max_ctx) {
   const b200_dlm_mixer& a = L.c.a;
-  const TileSig& s = h->sigs[L.sig];
+  bool mma = false;
+  if constexpr (sizeof(T) == 2) mma = h->attn_tc && L.sig_mma >= 0 && (h->max_entry_tokens > 1 || h->attn_tc > 1);      // single tokens: a 16-row fragment tile would be all padding
+  const TileSig& s = h->sigs[mma ? L.sig_mma : L.sig];
+  const int QT = mma ? 16 : L.QT, KT = mma ? 32 : L.KT;
   static bool attr_set = false;
   if (!attr_set) {
     B200_CUDA(cudaFuncSetAttribute(window_attn_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    B200_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    B200_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    B200_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
     attr_set = true;
   }
   WindowAttnParams p;
   p.q = h->qkv32; p.ldq = L.Nq + L.Nk + L.Nv; p.kcache = L.kcache; p.vcache = L.vcache; p.mix = L.mixhh; p.sink = L.sink;
   p.tile_row0 = h->meta_dev + s.off_row0; p.tile_rows = h->meta_dev + s.off_rows; p.tile_slot = h->meta_dev + s.off_slot;
   p.tok_pos = h->meta_dev + h->off_pos; p.out = h->obuf; p.part = h->part;
-  p.cap = h->cap; p.H = a.heads; p.G = a.kv_heads; p.dim = a.dim; p.vdim = a.vdim; p.window = a.window; p.QT = L.QT; p.KT = L.KT; p.kstride = L.kstride;
+  p.cap = h->cap; p.H = a.heads; p.G = a.kv_heads; p.dim = a.dim; p.vdim = a.vdim; p.window = a.window; p.QT = QT; p.KT = KT; p.kstride = L.kstride;
+  p.vec = ((size_t)L.Nk * sizeof(T)) % 16 == 0 && ((size_t)L.Nv * sizeof(T)) % 16 == 0;
   // keys are cut over several CTAs per tile when the tiles alone cannot fill the GPU (decoding, short portions)
-  const int key_tiles = ceil_div(std::min(a.window, max_ctx) + L.QT - 1, L.KT);
+  const int key_tiles = ceil_div(std::min(a.window, max_ctx) + QT - 1, KT);
   int nsplit = 1;
   if (h->attn_split > 0) nsplit = std::min(h->attn_split, 64);
   else if (s.count < 148) nsplit = std::min(std::max(296 / std::max(s.count, 1), 1), 64);
   nsplit = std::max(1, std::min(nsplit, key_tiles));
-  const int rpt = L.QT * a.heads;
+  const int rpt = QT * a.heads;
   while (nsplit > 1 && (size_t)s.count * nsplit * rpt * (a.vdim + 2) > h->part_floats) --nsplit;
   p.nsplit = nsplit;
-  B200_LAUNCH(window_attn_kernel<T>, dim3(s.count, nsplit), 256, L.attn_smem, h->stream, p);
+  if (mma) {
+    const dim3 grid(s.count, nsplit);
+    if (L.mma_items == 1) B200_LAUNCH(window_attn_mma_kernel<1>, grid, 256, L.mma_smem, h->stream, p);
+    else if (L.mma_items == 2) B200_LAUNCH(window_attn_mma_kernel<2>, grid, 256, L.mma_smem, h->stream, p);
+    else B200_LAUNCH(window_attn_mma_kernel<4>, grid, 256, L.mma_smem, h->stream, p);
+  } else {
+    B200_LAUNCH(window_attn_kernel<T>, dim3(s.count, nsplit), 256, L.attn_smem, h->stream, p);
+  }
   B200_TRY(check_launch("window_attn"));
   if (nsplit > 1) {
     float* merged = h->f32 ? static_cast<float*>(h->obuf) : h->attn32;
@@ -688,7 +726,7 @@ int step_sandwich(b200_dlm* h, int n_tok, int n_want, int max_ctx, float* logits
       sp.inv_tau = 1.f / b.tau; sp.cap = 0.f; sp.qscale = 1.f / sqrtf((float)b.dim); sp.St = L.St; sp.nvec = nullptr; sp.mval = nullptr;
       sp.ent_tok0 = meta + h->off_ent_tok0; sp.ent_ntok = meta + h->off_ent_ntok; sp.ent_slot = meta + h->off_ent_slot; sp.ent_pos0 = meta + h->off_ent_pos0;
       sp.out = h->scan32; sp.heads = b.heads; sp.dim = b.dim; sp.vdim = b.vdim;
-      TIMED(CLS_RECURRENT, B200_TRY((launch_scan<T, MODE_DECAY>(st, sp, h->n_entries))));
+      TIMED(CLS_RECURRENT, B200_TRY((launch_scan<T, MODE_DECAY>(h, sp, n_tok))));
       const long long rows = (long long)n_tok * b.heads;
       TIMED(CLS_ELEMENTWISE, B200_LAUNCH(head_norm_gate_kernel<T>, (unsigned)ceil_div64(rows, 4), 128, 0, st, h->scan32, L.rnorm, 0, proj, (long long)L.ldp, L.r_g, 1, ob2,
                                          b.heads, b.vdim, rows, c.norm_eps));
@@ -704,7 +742,7 @@ int step_sandwich(b200_dlm* h, int n_tok, int n_want, int max_ctx, float* logits
       sp.inv_tau = 0.f; sp.cap = a.gate_cap; sp.qscale = 1.f / sqrtf((float)a.dim); sp.St = L.St; sp.nvec = L.nvec; sp.mval = L.mval;
       sp.ent_tok0 = meta + h->off_ent_tok0; sp.ent_ntok = meta + h->off_ent_ntok; sp.ent_slot = meta + h->off_ent_slot; sp.ent_pos0 = meta + h->off_ent_pos0;
       sp.out = h->scan32; sp.heads = a.heads; sp.dim = a.dim; sp.vdim = a.vdim;
-      TIMED(CLS_RECURRENT, B200_TRY((launch_scan<T, MODE_EXPGATE>(st, sp, h->n_entries))));
+      TIMED(CLS_RECURRENT, B200_TRY((launch_scan<T, MODE_EXPGATE>(h, sp, n_tok))));
       const long long rows = (long long)n_tok * a.heads;
       TIMED(CLS_ELEMENTWISE, B200_LAUNCH(head_norm_gate_kernel<T>, (unsigned)ceil_div64(rows, 4), 128, 0, st, h->scan32, L.rnorm, a.vdim, proj, (long long)L.ldp, L.r_g, 0, ob2,
                                          a.heads, a.vdim, rows, c.norm_eps));
@@ -807,7 +845,7 @@ int b200_dlm_set_option(b200_dlm* h, const char* name, int value) {
     if (h->slots) B200_FAIL(B200_ERR_STATE, "dlm_set_option: trace_layers must be set before cache_begin");
     h->trace_layers = value != 0;
   } else if (n == "attn_tc") {
-    h->attn_tc = value != 0;
+    h->attn_tc = value < 0 ? 0 : value;      // 2: the tensor-core window attention also for single-token requests
   } else if (n == "time_kernels") {
     h->time_kernels = value != 0;
   } else if (n == "attn_split") {
@@ -947,7 +985,7 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
   const size_t T = (size_t)max_step_tokens, W = (size_t)c.width;
   h->stream = static_cast<cudaStream_t>(stream);
   const bool sandwich = c.block == B200_BLOCK_SANDWICH;
-  size_t max_ldp = 0, max_hr = 0, max_hv = 0, max_ff = 1, max_r = 0, max_tiles = 0, max_qkv = 1, max_rv = 1, max_gate = 1, max_e = 1, max_top = 0, max_part = 0;
+  size_t max_ldp = 0, max_hr = 0, max_hv = 0, max_ff = 1, max_r = 0, max_tiles = 0, max_qkv = 1, max_rv = 1, max_gate = 1, max_e = 1, max_top = 0, max_part = 0, max_prep = 4;
   for (auto& L : h->layers) {
     const b200_dlm_mixer &a = L.c.a, &b = L.c.b;
     max_ldp = std::max(max_ldp, (size_t)L.ldp);
@@ -970,7 +1008,8 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
       max_qkv = std::max(max_qkv, C);
       max_rv = std::max(max_rv, (size_t)b.heads * b.vdim);
       max_gate = std::max(max_gate, (size_t)b.heads * b.dim);
-      max_part = std::max(max_part, (size_t)L.QT * a.heads * (a.vdim + 2));
+      max_prep = std::max(max_prep, (size_t)b.heads * (3 * b.dim + 4));
+      max_part = std::max(max_part, (size_t)(L.sig_mma >= 0 ? 16 : L.QT) * a.heads * (a.vdim + 2));
     } else {
       const size_t slices = (size_t)ceil_div(a.vdim, 16);
       B200_TRY(A.alloc_t(&L.St, (size_t)slots * a.heads * a.vdim * a.dim));
@@ -978,6 +1017,7 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
       B200_TRY(A.alloc_t(&L.mval, (size_t)slots * a.heads * slices));
       max_rv = std::max(max_rv, (size_t)a.heads * a.vdim);
       max_gate = std::max(max_gate, (size_t)2 * a.heads);
+      max_prep = std::max(max_prep, (size_t)a.heads * (2 * a.dim + 8));
     }
     if (L.c.mlp == B200_MLP_MOE_RELU2) { max_e = std::max(max_e, (size_t)L.c.experts); max_top = std::max(max_top, (size_t)L.c.top); }
   }
@@ -992,6 +1032,8 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
     B200_TRY(A.alloc_t(&h->h32, T * W));
     B200_TRY(A.alloc_t(&h->qkv32, T * max_qkv));
     B200_TRY(A.alloc_t(&h->scan32, T * max_rv));
+    B200_TRY(A.alloc_t(&h->scan_v, T * max_rv));
+    B200_TRY(A.alloc_t(&h->scan_prep, T * max_prep));
     B200_TRY(A.alloc_t(&h->gate32, T * max_gate));
     B200_TRY(A.alloc_t(&h->attn32, T * max_hv));
     B200_TRY(A.alloc(&h->obuf2, T * max_rv * es));
@@ -1120,6 +1162,8 @@ int b200_dlm_step(b200_dlm* h, int n_entries, const int32_t* slots_host, const i
   B200_CUDA(cudaMemcpyAsync(h->meta_dev, m, (size_t)h->meta_ints * sizeof(int), cudaMemcpyHostToDevice, h->stream));
   B200_CUDA(cudaEventRecord(h->ev_meta, h->stream));
   h->n_entries = n_entries;
+  h->max_entry_tokens = 0;
+  for (int e = 0; e < n_entries; ++e) h->max_entry_tokens = std::max(h->max_entry_tokens, (int)counts_host[e]);
   int rc;
   if (h->cfg.block == B200_BLOCK_SANDWICH) rc = h->f32 ? step_sandwich<float>(h, t, n_want, max_ctx, logits_dev) : step_sandwich<bf16>(h, t, n_want, max_ctx, logits_dev);
   else rc = h->f32 ? step_body<float>(h, t, n_want, max_ctx, logits_dev) : step_body<bf16>(h, t, n_want, max_ctx, logits_dev);

@@ -174,6 +174,7 @@ struct WindowAttnParams {
   void* out;                // T [tokens][H * vdim]
   float* part;              // nsplit > 1: [tile][split][QT * H][vdim + 2]
   int cap, H, G, dim, vdim, window, QT, KT, nsplit, kstride;      // kstride: elements between staged key rows (odd number of words)
+  int vec;                  // key and value rows are multiples of 16 bytes: staged with 16-byte loads
 };
 
 template <typename T>
@@ -189,8 +190,8 @@ __global__ void __launch_bounds__(256) window_attn_kernel(WindowAttnParams p) {
   float* rm = mixs + H * H;                                        // [QT * H] running maximum
   float* rl = rm + QT * H;                                         // [QT * H] running sum
   float* rc = rl + QT * H;                                         // [QT * H] rescale factor of the current key tile
-  T* ks = reinterpret_cast<T*>(rc + QT * H);                       // [KT][kstride]
-  T* vs = ks + (size_t)KT * p.kstride;                             // [KT][Nv]
+  T* vs = reinterpret_cast<T*>(smem_raw + (((size_t)((rc + QT * H) - qs) * 4 + 15) / 16) * 16);     // [KT][Nv], on 16 bytes
+  T* ks = vs + (size_t)KT * Nv;                                    // [KT][kstride]
   const int tile = blockIdx.x, split = blockIdx.y;
   const int tok0 = p.tile_row0[tile] / H, nt = p.tile_rows[tile] / H;
   const int p0 = p.tok_pos[tok0];                                  // positions p0 .. p0 + nt - 1
@@ -217,8 +218,25 @@ __global__ void __launch_bounds__(256) window_attn_kernel(WindowAttnParams p) {
     const int kb = kmin + kt * KT;
     const int nk = min(KT, kmax + 1 - kb);
     __syncthreads();
-    for (int i = threadIdx.x; i < nk * Nk; i += 256) { const int j = i / Nk, e = i - j * Nk; ks[j * p.kstride + e] = kc[(long long)(kb + j) * Nk + e]; }
-    for (int i = threadIdx.x; i < nk * Nv; i += 256) vs[i] = vc[(long long)kb * Nv + i];
+    if (p.vec) {        // rows start on 16 bytes in the cache: 16-byte loads, 4-byte stores into the (odd-word strided) key rows
+      const int kw = Nk * (int)sizeof(T) / 16, vw = Nv * (int)sizeof(T) / 16;
+      const uint4* k4 = reinterpret_cast<const uint4*>(kc + (long long)kb * Nk);
+      const uint4* v4 = reinterpret_cast<const uint4*>(vc + (long long)kb * Nv);
+      uint32_t* ksw = reinterpret_cast<uint32_t*>(ks);
+      const int kstw = p.kstride * (int)sizeof(T) / 4;
+#pragma unroll 4
+      for (int i = threadIdx.x; i < nk * kw; i += 256) {
+        const int j = i / kw, e = i - j * kw;
+        const uint4 v = k4[i];
+        uint32_t* d = ksw + j * kstw + e * 4;
+        d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+      }
+#pragma unroll 4
+      for (int i = threadIdx.x; i < nk * vw; i += 256) reinterpret_cast<uint4*>(vs)[i] = v4[i];
+    } else {
+      for (int i = threadIdx.x; i < nk * Nk; i += 256) { const int j = i / Nk, e = i - j * Nk; ks[j * p.kstride + e] = kc[(long long)(kb + j) * Nk + e]; }
+      for (int i = threadIdx.x; i < nk * Nv; i += 256) vs[i] = vc[(long long)kb * Nv + i];
+    }
     __syncthreads();
     // raw scores: item (row = qt * H + h, key j), keys fastest
     for (int i = threadIdx.x; i < QT * H * KT; i += 256) {
@@ -233,7 +251,7 @@ __global__ void __launch_bounds__(256) window_attn_kernel(WindowAttnParams p) {
     }
     __syncthreads();
     // mix over heads, mask, online softmax: one warp per row, lanes over keys
-    for (int row = warp; row < QT * H; row += 8) {
+    for (int row = warp; row < nt * H; row += 8) {
       const int qt = row / H, h = row - qt * H;
       const int pos = p0 + qt;
       float mx = -INFINITY;
@@ -266,7 +284,7 @@ __global__ void __launch_bounds__(256) window_attn_kernel(WindowAttnParams p) {
     }
     __syncthreads();
     // weighted sum of the values: item (row, c), c fastest
-    for (int i = threadIdx.x; i < QT * H * vdim; i += 256) {
+    for (int i = threadIdx.x; i < nt * H * vdim; i += 256) {
       const int row = i / vdim, c = i - row * vdim;
       const T* vv = vs + ((row % H) / rep) * vdim + c;
       const float* w = sp + row * KS;
@@ -283,6 +301,179 @@ __global__ void __launch_bounds__(256) window_attn_kernel(WindowAttnParams p) {
     float* dst = p.part + ((long long)tile * p.nsplit + split) * (QT * H) * (vdim + 2);
     for (int i = threadIdx.x; i < nt * H * vdim; i += 256) { const int row = i / vdim; dst[(long long)row * (vdim + 2) + (i - row * vdim)] = oacc[i]; }
     for (int row = threadIdx.x; row < nt * H; row += 256) { dst[(long long)row * (vdim + 2) + vdim] = rm[row]; dst[(long long)row * (vdim + 2) + vdim + 1] = rl[row]; }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// The same attention on the tensor cores for bf16 caches (dim and vdim multiples of 16): a tile is 16 consecutive tokens of one
+// request with all H heads, a key tile 32 keys.  Per key tile: (1) raw scores Q_h K_g^T per head as mma.sync m16n8k16 (queries
+// rounded to bf16 once, fp32 accumulate) into shared memory; (2) head mix, window mask and online softmax in fp32, one warp
+// per (head, token) row, the weights going back as bf16; (3) O_h += P_h V_g on the tensor cores, the accumulators of a warp's
+// NI items (head, 64 value columns) in registers.  Split keys and the sink as in window_attn_kernel; rows of `part` are
+// (token, head) pairs, head fastest, as latent_attn_merge_kernel wants them.
+// ---------------------------------------------------------------------------------------------------------------------------
+template <int NI>
+__global__ void __launch_bounds__(256) window_attn_mma_kernel(WindowAttnParams p) {
+  constexpr int QT = 16, KT = 32, SS = 40, PS = 40;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int H = p.H, G = p.G, dim = p.dim, vdim = p.vdim, rep = H / G;
+  const int Nq = H * dim, Nk = G * dim, Nv = G * vdim, QS = Nq + 8, KS = Nk + 8, VS = Nv + 8, VC = (vdim + 63) / 64;
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                   // [16][QS]
+  bf16* Ks = Qs + QT * QS;                                        // [32][KS]
+  bf16* Vs = Ks + KT * KS;                                        // [32][VS]
+  bf16* pb = Vs + KT * VS;                                        // [H][16][PS] softmax weights of the key tile
+  float* sraw = reinterpret_cast<float*>(pb + H * QT * PS);       // [H][16][SS] raw scores
+  float* mixs = sraw + H * QT * SS;                               // [H][H]
+  float* rm = mixs + H * H;                                       // [H * 16] running maximum, row = h * 16 + token
+  float* rl = rm + H * QT;
+  float* rc = rl + H * QT;
+  const int tile = blockIdx.x, split = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g8 = lane >> 2, t4 = lane & 3, mi = lane >> 3;
+  const int tok0 = p.tile_row0[tile] / H, nt = p.tile_rows[tile] / H;
+  const int p0 = p.tok_pos[tok0];
+  const bf16* kc = static_cast<const bf16*>(p.kcache) + (long long)p.tile_slot[tile] * p.cap * Nk;
+  const bf16* vc = static_cast<const bf16*>(p.vcache) + (long long)p.tile_slot[tile] * p.cap * Nv;
+  const int kmin = max(0, p0 - p.window + 1), kmax = p0 + nt - 1;
+  const int n_kt = (kmax - kmin) / KT + 1;
+  const int per = (n_kt + p.nsplit - 1) / p.nsplit;
+  const int kt0 = split * per, kt1 = min(n_kt, kt0 + per);
+
+  for (int i = threadIdx.x; i < QT * (Nq / 2); i += 256) {
+    const int qt = i / (Nq / 2), e = (i - qt * (Nq / 2)) * 2;
+    float2 v = make_float2(0.f, 0.f);
+    if (qt < nt) v = *reinterpret_cast<const float2*>(p.q + (long long)(tok0 + qt) * p.ldq + e);
+    *reinterpret_cast<unsigned*>(Qs + qt * QS + e) = pack_bf16(v.x, v.y);
+  }
+  for (int i = threadIdx.x; i < H * H; i += 256) mixs[i] = p.mix[i];
+  for (int i = threadIdx.x; i < H * QT; i += 256) {
+    if (split == 0) { rm[i] = p.sink[i / QT]; rl[i] = 1.f; }
+    else { rm[i] = -INFINITY; rl[i] = 0.f; }
+  }
+  float oacc[NI][8][4];
+#pragma unroll
+  for (int a = 0; a < NI; ++a)
+#pragma unroll
+    for (int b = 0; b < 8; ++b) { oacc[a][b][0] = oacc[a][b][1] = oacc[a][b][2] = oacc[a][b][3] = 0.f; }
+
+  for (int kt = kt0; kt < kt1; ++kt) {
+    const int kb = kmin + kt * KT;
+    const int nk = min(KT, kmax + 1 - kb);
+    __syncthreads();
+    {   // keys and values of the tile: 16-byte loads; rows past the last key are zero (their weights are zero, they must be finite)
+      const int kw = Nk / 8, vw = Nv / 8;
+      const uint4* k4 = reinterpret_cast<const uint4*>(kc + (long long)kb * Nk);
+      const uint4* v4 = reinterpret_cast<const uint4*>(vc + (long long)kb * Nv);
+#pragma unroll 4
+      for (int i = threadIdx.x; i < KT * kw; i += 256) {
+        const int j = i / kw, e = i - j * kw;
+        *reinterpret_cast<uint4*>(Ks + j * KS + e * 8) = j < nk ? k4[i] : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll 4
+      for (int i = threadIdx.x; i < KT * vw; i += 256) {
+        const int j = i / vw, e = i - j * vw;
+        *reinterpret_cast<uint4*>(Vs + j * VS + e * 8) = j < nk ? v4[i] : make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    __syncthreads();
+    // (1) raw scores, one head at a time per warp
+    for (int h = warp; h < H; h += 8) {
+      const bf16* qh = Qs + h * dim;
+      const bf16* kh = Ks + (h / rep) * dim;
+      float sacc[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f; }
+      for (int ks = 0; ks < dim / 16; ++ks) {
+        unsigned a[4];
+        ldmatrix_x4(a, qh + ((mi & 1) * 8 + (lane & 7)) * QS + ks * 16 + (mi >> 1) * 8);
+#pragma unroll
+        for (int np = 0; np < 2; ++np) {
+          unsigned b[4];
+          ldmatrix_x4(b, kh + (np * 16 + (mi >> 1) * 8 + (lane & 7)) * KS + ks * 16 + (mi & 1) * 8);
+          mma_bf16_16816(sacc[2 * np], a, b[0], b[1]);
+          mma_bf16_16816(sacc[2 * np + 1], a, b[2], b[3]);
+        }
+      }
+      float* dst = sraw + h * QT * SS;
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb) {
+        *reinterpret_cast<float2*>(dst + g8 * SS + nb * 8 + 2 * t4) = make_float2(sacc[nb][0], sacc[nb][1]);
+        *reinterpret_cast<float2*>(dst + (g8 + 8) * SS + nb * 8 + 2 * t4) = make_float2(sacc[nb][2], sacc[nb][3]);
+      }
+    }
+    __syncthreads();
+    // (2) mix over heads, mask, online softmax; lane = key
+    for (int row = warp; row < H * QT; row += 8) {
+      const int h = row / QT, qt = row - h * QT;
+      const int pos = p0 + qt, kj = kb + lane;
+      float s = -INFINITY;
+      if (lane < nk && qt < nt && kj <= pos && pos - kj < p.window) {
+        s = 0.f;
+        for (int g = 0; g < H; ++g) s = fmaf(mixs[h * H + g], sraw[(g * QT + qt) * SS + lane], s);
+      }
+      const float mo = rm[row], mn = fmaxf(mo, warp_max(s));
+      const float w = s > -INFINITY ? expf(s - mn) : 0.f;
+      const float sum = warp_sum(w);
+      pb[row * PS + lane] = __float2bfloat16_rn(w);
+      if (lane == 0) {
+        const float corr = mn > -INFINITY ? expf(mo - mn) : 1.f;
+        rc[row] = corr;
+        rl[row] = rl[row] * corr + sum;
+        rm[row] = mn;
+      }
+    }
+    __syncthreads();
+    // (3) weighted sums of the values
+#pragma unroll
+    for (int ii = 0; ii < NI; ++ii) {
+      const int it = warp + 8 * ii;
+      if (it >= H * VC) break;
+      const int h = it / VC, c0 = (it - h * VC) * 64;
+      const float corr0 = rc[h * QT + g8], corr1 = rc[h * QT + g8 + 8];
+#pragma unroll
+      for (int nb = 0; nb < 8; ++nb) { oacc[ii][nb][0] *= corr0; oacc[ii][nb][1] *= corr0; oacc[ii][nb][2] *= corr1; oacc[ii][nb][3] *= corr1; }
+      const bf16* vh = Vs + (h / rep) * vdim + c0;
+#pragma unroll
+      for (int k2 = 0; k2 < 2; ++k2) {
+        unsigned pf[4];
+        ldmatrix_x4(pf, pb + h * QT * PS + ((lane & 7) + 8 * ((lane >> 3) & 1)) * PS + 16 * k2 + 8 * (lane >> 4));
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+          if (c0 + np * 16 < vdim) {
+            unsigned b[4];
+            ldmatrix_x4_trans(b, vh + (k2 * 16 + (mi & 1) * 8 + (lane & 7)) * VS + np * 16 + (mi >> 1) * 8);
+            mma_bf16_16816(oacc[ii][2 * np], pf, b[0], b[1]);
+            mma_bf16_16816(oacc[ii][2 * np + 1], pf, b[2], b[3]);
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int ii = 0; ii < NI; ++ii) {
+    const int it = warp + 8 * ii;
+    if (it >= H * VC) break;
+    const int h = it / VC, c0 = (it - h * VC) * 64;
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int qt = g8 + 8 * hf;
+      if (qt >= nt) continue;
+      if (p.nsplit == 1) {
+        const float inv = 1.f / rl[h * QT + qt];
+        bf16* dst = static_cast<bf16*>(p.out) + ((long long)(tok0 + qt) * H + h) * vdim + c0;
+#pragma unroll
+        for (int nb = 0; nb < 8; ++nb)
+          if (c0 + nb * 8 < vdim)
+            *reinterpret_cast<unsigned*>(dst + nb * 8 + 2 * t4) = pack_bf16(oacc[ii][nb][2 * hf] * inv, oacc[ii][nb][2 * hf + 1] * inv);
+      } else {
+        float* dst = p.part + (((long long)tile * p.nsplit + split) * (QT * H) + qt * H + h) * (vdim + 2);
+#pragma unroll
+        for (int nb = 0; nb < 8; ++nb)
+          if (c0 + nb * 8 < vdim)
+            *reinterpret_cast<float2*>(dst + c0 + nb * 8 + 2 * t4) = make_float2(oacc[ii][nb][2 * hf], oacc[ii][nb][2 * hf + 1]);
+        if (c0 == 0 && t4 == 0) { dst[vdim] = rm[h * QT + qt]; dst[vdim + 1] = rl[h * QT + qt]; }
+      }
+    }
   }
 }
 
@@ -322,9 +513,7 @@ __global__ void __launch_bounds__(256) small_proj_f32_kernel(const T* __restrict
 //       i_t = cap tanh(gi / cap), f_t = logsigmoid(cap tanh(gf / cap)),  m_t = max(f_t + m_{t-1}, i_t)   (m starts at 0)
 //       S <- e^(f_t + m_{t-1} - m_t) S + e^(i_t - m_t) k_t v_t^T,  n likewise with k_t alone
 //       o_t = S^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6)
-// q is scaled by qscale.  A CTA owns 16 columns of one (request, head) and walks the request's new tokens in order; lane & 7
-// selects a group of rows (row = group + 8 i), so a column's dot product with q closes with three shuffles.  Tokens are staged
-// in shared memory TT at a time.  Grid: (entries * heads, ceil(vdim / 16)).
+// q is scaled by qscale.  scan_prep_kernel lays out what a token contributes; matrix_memory_scan_kernel runs the recurrence.
 // ---------------------------------------------------------------------------------------------------------------------------
 enum { MODE_DECAY = 0, MODE_EXPGATE = 1 };
 
@@ -335,6 +524,9 @@ struct ScanParams {
   const float* z;           // MODE_DECAY: [tokens][heads * dim] decay logits;  MODE_EXPGATE: [tokens][2 * heads] gate inputs (i then f, biased)
   const float* zb;          // MODE_DECAY: bias [heads * dim]
   float inv_tau, cap, qscale;
+  float* prep;              // [tokens][heads][nvec * dim (+ 2 gates, padded to 4)] fp32: what the recurrence reads per token and head
+  float* vprep;             // [tokens][heads * vdim] fp32
+  int prow;                 // floats per (token, head) row of prep
   float* St;                // [slots][heads][vdim][dim]
   float* nvec;              // MODE_EXPGATE: [slots][heads][column slices][dim]: every CTA of a head carries its own copy of n and m,
   float* mval;              // MODE_EXPGATE: [slots][heads][column slices]        so that none reads what another has already replaced
@@ -343,19 +535,52 @@ struct ScanParams {
   const int* ent_slot;
   const int* ent_pos0;
   float* out;               // [tokens][heads * vdim]
-  int heads, dim, vdim;
+  int heads, dim, vdim, stage, vec;      // vec: rows of prep and the 16-column slices of vprep start on 16 bytes
 };
 
-template <typename T, int MODE, int R>      // R rows per thread: dim <= 8 * R
+// Everything the recurrence reads, as fp32 rows that its CTAs can copy asynchronously: per (token, head)
+//   MODE_DECAY:   [q * qscale | k | a = sigmoid(z + bz)^(1 / tau)]
+//   MODE_EXPGATE: [q * qscale | k | i, f]   with i = cap tanh(gi / cap), f = logsigmoid(cap tanh(gf / cap))
+// and the values as fp32.  One CTA per token.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) scan_prep_kernel(ScanParams p) {
+  const long long t = blockIdx.x;
+  const int heads = p.heads, dim = p.dim;
+  const T* row = static_cast<const T*>(p.proj) + t * p.ld;
+  float* dst = p.prep + t * heads * p.prow;
+  for (int i = threadIdx.x; i < heads * dim; i += 256) {
+    const int h = i / dim, d = i - h * dim;
+    float* o = dst + h * p.prow;
+    o[d] = to_f(row[p.off_q + i]) * p.qscale;
+    o[dim + d] = to_f(row[p.off_k + i]);
+    if (MODE == MODE_DECAY) o[2 * dim + d] = expf(log_sigmoidf(p.z[t * heads * dim + i] + p.zb[i]) * p.inv_tau);
+  }
+  if (MODE == MODE_EXPGATE) {
+    for (int i = threadIdx.x; i < 2 * heads; i += 256) {
+      const int which = i / heads, h = i - which * heads;
+      const float g = p.cap * tanhf(p.z[t * 2 * heads + i] / p.cap);
+      dst[h * p.prow + 2 * dim + which] = which ? log_sigmoidf(g) : g;
+    }
+  }
+  for (int i = threadIdx.x; i < heads * p.vdim; i += 256) p.vprep[t * heads * p.vdim + i] = to_f(row[p.off_v + i]);
+}
+
+__device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* src, bool vec4) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+  if (vec4) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+  else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+
+// The recurrence itself.  A CTA owns 16 columns of one (request, head) and walks the request's new tokens in order; lane & 7
+// selects a group of rows (row = group + 8 i), so a column's dot product with q closes with three shuffles.  Tokens arrive in
+// stages of `stage` tokens, copied asynchronously into one of two shared-memory buffers while the other is being consumed.
+// Grid: (entries * heads, ceil(vdim / 16)).
+template <int MODE, int R>      // R rows per thread: dim <= 8 * R
 __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
-  constexpr int TT = 8;
-  extern __shared__ float sm[];
-  const int dim = p.dim, vdim = p.vdim, heads = p.heads;
-  float* ksm = sm;                      // [TT][dim]
-  float* qsm = ksm + TT * dim;          // [TT][dim]
-  float* asm_ = qsm + TT * dim;         // [TT][dim] decay factors (MODE_DECAY)
-  float* vsm = asm_ + TT * dim;         // [TT][16]
-  float* gsm = vsm + TT * 16;           // [TT][2] gate inputs (MODE_EXPGATE)
+  const int TT = p.stage;
+  extern __shared__ __align__(16) float sm[];
+  const int dim = p.dim, vdim = p.vdim, heads = p.heads, prow = p.prow;
+  const int srow = prow + 16;                         // a staged token: its prep row, then its 16 values
   const int ent = blockIdx.x / heads, head = blockIdx.x - ent * heads;
   const int tok0 = p.ent_tok0[ent], nt = p.ent_ntok[ent], slot = p.ent_slot[ent], pos0 = p.ent_pos0[ent];
   const int rg = threadIdx.x & 7, cl = threadIdx.x >> 3, col = blockIdx.y * 16 + cl;
@@ -372,35 +597,45 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
     nv[i] = (MODE == MODE_EXPGATE && live) ? nst[r] : 0.f;
   }
   if (MODE == MODE_EXPGATE && pos0 > 0) m = p.mval[slice];
-  const T* proj = static_cast<const T*>(p.proj);
 
-  for (int t0 = 0; t0 < nt; t0 += TT) {
+  auto issue = [&](int t0, int buf) {
     const int tn = min(TT, nt - t0);
+    float* base = sm + buf * TT * srow;
+    if (p.vec) {
+      const int pw = prow / 4;
+      for (int i = threadIdx.x; i < tn * (pw + 4); i += 128) {
+        const int tt = i / (pw + 4), e = i - tt * (pw + 4);
+        const long long tok = tok0 + t0 + tt;
+        if (e < pw) cp_async_f32(base + tt * srow + e * 4, p.prep + (tok * heads + head) * prow + e * 4, true);
+        else if (blockIdx.y * 16 + (e - pw) * 4 < vdim) cp_async_f32(base + tt * srow + prow + (e - pw) * 4, p.vprep + tok * heads * vdim + head * vdim + blockIdx.y * 16 + (e - pw) * 4, true);
+      }
+    } else {
+      for (int i = threadIdx.x; i < tn * srow; i += 128) {
+        const int tt = i / srow, e = i - tt * srow;
+        const long long tok = tok0 + t0 + tt;
+        if (e < prow) cp_async_f32(base + tt * srow + e, p.prep + (tok * heads + head) * prow + e, false);
+        else if (blockIdx.y * 16 + (e - prow) < vdim) cp_async_f32(base + tt * srow + e, p.vprep + tok * heads * vdim + head * vdim + blockIdx.y * 16 + (e - prow), false);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  issue(0, 0);
+  for (int t0 = 0, st = 0; t0 < nt; t0 += TT, ++st) {
+    const int tn = min(TT, nt - t0);
+    if (t0 + TT < nt) { issue(t0 + TT, (st + 1) & 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+    else asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    for (int i = threadIdx.x; i < tn * dim; i += 128) {
-      const int tt = i / dim, d = i - tt * dim;
-      const long long row = (long long)(tok0 + t0 + tt);
-      ksm[i] = to_f(proj[row * p.ld + p.off_k + head * dim + d]);
-      qsm[i] = to_f(proj[row * p.ld + p.off_q + head * dim + d]) * p.qscale;
-      if (MODE == MODE_DECAY) asm_[i] = expf(log_sigmoidf(p.z[row * heads * dim + head * dim + d] + p.zb[head * dim + d]) * p.inv_tau);
-    }
-    for (int i = threadIdx.x; i < tn * 16; i += 128) {
-      const int tt = i >> 4, c = blockIdx.y * 16 + (i & 15);
-      vsm[i] = c < vdim ? to_f(proj[(long long)(tok0 + t0 + tt) * p.ld + p.off_v + head * vdim + c]) : 0.f;
-    }
-    if (MODE == MODE_EXPGATE && threadIdx.x < tn * 2) {
-      const int tt = threadIdx.x >> 1, which = threadIdx.x & 1;
-      gsm[threadIdx.x] = p.z[(long long)(tok0 + t0 + tt) * 2 * heads + which * heads + head];
-    }
-    __syncthreads();
+    const float* base = sm + (st & 1) * TT * srow;
+#pragma unroll 4
     for (int tt = 0; tt < tn; ++tt) {
-      const float v = vsm[tt * 16 + cl];
-      const float* kk = ksm + tt * dim;
-      const float* qq = qsm + tt * dim;
-      float acc = 0.f, nq = 0.f, fa = 1.f, fb = 1.f, m2 = 0.f;
+      const float* qq = base + tt * srow;
+      const float* kk = qq + dim;
+      const float* aa = kk + dim;
+      const float v = col_ok ? qq[prow + cl] : 0.f;
+      float acc = 0.f, acc1 = 0.f, nq = 0.f, fa = 1.f, fb = 1.f, m2 = 0.f;
       if (MODE == MODE_EXPGATE) {
-        const float il = p.cap * tanhf(gsm[2 * tt] / p.cap);
-        const float fl = log_sigmoidf(p.cap * tanhf(gsm[2 * tt + 1] / p.cap));
+        const float il = aa[0], fl = aa[1];
         m2 = fmaxf(fl + m, il);
         fa = expf(fl + m - m2);
         fb = expf(il - m2);
@@ -412,15 +647,16 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
         if (r < dim) {
           const float kv = kk[r], qv = qq[r];
           if (MODE == MODE_DECAY) {
-            S[i] = fmaf(asm_[tt * dim + r], S[i], kv * v);
+            S[i] = fmaf(aa[r], S[i], kv * v);
           } else {
             S[i] = fmaf(fa, S[i], fb * kv * v);
             nv[i] = fmaf(fa, nv[i], fb * kv);
             nq = fmaf(nv[i], qv, nq);
           }
-          acc = fmaf(S[i], qv, acc);
+          if (i & 1) acc1 = fmaf(S[i], qv, acc1); else acc = fmaf(S[i], qv, acc);
         }
       }
+      acc += acc1;
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
       acc += __shfl_xor_sync(0xffffffffu, acc, 4);
@@ -432,6 +668,7 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
       }
       if (rg == 0 && col_ok) p.out[(long long)(tok0 + t0 + tt) * heads * vdim + head * vdim + col] = acc;
     }
+    __syncthreads();
   }
 #pragma unroll
   for (int i = 0; i < R; ++i) {
