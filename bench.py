@@ -692,7 +692,7 @@ def decoder_lm_arm(args) -> None:
 GOVUVIK_SIZES = {
     # name: (width, layers, attention heads, kv heads, head dim, window, recurrent heads, key dim, value dim, experts, top, expert ff, vocab)
     "w2048": (2048, 4, 16, 4, 128, 1024, 8, 128, 256, 16, 2, 4096, 32000),
-    "w4096": (4096, 2, 32, 8, 128, 1024, 16, 128, 256, 16, 2, 8192, 32000),
+    "w4096": (4096, 2, 16, 4, 128, 1024, 16, 128, 256, 16, 2, 8192, 32000),
 }
 
 

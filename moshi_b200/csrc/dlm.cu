@@ -37,7 +37,8 @@ struct Layer {
   // window attention (a)
   int a_q = 0, a_k = 0, a_v = 0, a_g = 0;         // offsets into the concatenated projection
   int Nq = 0, Nk = 0, Nv = 0, QT = 0, KT = 0, kstride = 0; size_t attn_smem = 0;
-  int sig_mma = -1, mma_items = 0; size_t mma_smem = 0;      // tensor-core window attention: tile list of 16 tokens, items per warp
+  int sig_mma = -1, mma_items = 0; size_t mma_smem = 0;
+  int sig_one = -1, KT_one = 0, kstride_one = 0; size_t smem_one = 0;      // single-token requests: tiles of one token, less shared memory, more CTAs per SM      // tensor-core window attention: tile list of 16 tokens, items per warp
   float *qnorm = nullptr, *knorm = nullptr, *qkv_conv = nullptr, *qkv_hist = nullptr, *mixhh = nullptr; double* freq = nullptr;
   void *kcache = nullptr, *vcache = nullptr;
   Weight a_o;
@@ -495,6 +496,11 @@ int finalize_sandwich_layer(b200_dlm* h, int i, std::vector<void*>& drop) {
     }
     if (!L.QT) B200_FAIL(B200_ERR_SHAPE, "decoder LM: layer %d: the window attention's heads do not fit shared memory", i);
     L.sig = add_sig(h, a.heads, L.QT * a.heads);
+    for (int kt : {32, 16, 8}) {
+      int ks = 0;
+      const size_t sm = window_attn_smem(a, 1, kt, es, &ks);
+      if (sm <= 200 * 1024) { L.sig_one = add_sig(h, a.heads, a.heads); L.KT_one = kt; L.kstride_one = ks; L.smem_one = sm; break; }
+    }
     if (!h->f32 && a.dim % 16 == 0 && a.vdim % 16 == 0) {     // bf16 cache, fragment-sized heads: the tensor-core kernel, if it fits
       const size_t Hh = a.heads, QS = L.Nq + 8, KS = L.Nk + 8, VS = L.Nv + 8;
       const size_t sm = 2 * (16 * QS + 32 * KS + 32 * VS + Hh * 16 * 40) + 4 * (Hh * 16 * 40 + Hh * Hh + 3 * Hh * 16);
@@ -593,8 +599,9 @@ int window_attention(b200_dlm* h, const Layer& L, int n_tok, int max_ctx) {
   const b200_dlm_mixer& a = L.c.a;
   bool mma = false;
   if constexpr (sizeof(T) == 2) mma = h->attn_tc && L.sig_mma >= 0 && (h->max_entry_tokens > 1 || h->attn_tc > 1);      // single tokens: a 16-row fragment tile would be all padding
-  const TileSig& s = h->sigs[mma ? L.sig_mma : L.sig];
-  const int QT = mma ? 16 : L.QT, KT = mma ? 32 : L.KT;
+  const bool one = !mma && h->max_entry_tokens == 1 && L.sig_one >= 0;
+  const TileSig& s = h->sigs[mma ? L.sig_mma : one ? L.sig_one : L.sig];
+  const int QT = mma ? 16 : one ? 1 : L.QT, KT = mma ? 32 : one ? L.KT_one : L.KT;
   static bool attr_set = false;
   if (!attr_set) {
     B200_CUDA(cudaFuncSetAttribute(window_attn_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -607,13 +614,13 @@ int window_attention(b200_dlm* h, const Layer& L, int n_tok, int max_ctx) {
   p.q = h->qkv32; p.ldq = L.Nq + L.Nk + L.Nv; p.kcache = L.kcache; p.vcache = L.vcache; p.mix = L.mixhh; p.sink = L.sink;
   p.tile_row0 = h->meta_dev + s.off_row0; p.tile_rows = h->meta_dev + s.off_rows; p.tile_slot = h->meta_dev + s.off_slot;
   p.tok_pos = h->meta_dev + h->off_pos; p.out = h->obuf; p.part = h->part;
-  p.cap = h->cap; p.H = a.heads; p.G = a.kv_heads; p.dim = a.dim; p.vdim = a.vdim; p.window = a.window; p.QT = QT; p.KT = KT; p.kstride = L.kstride;
+  p.cap = h->cap; p.H = a.heads; p.G = a.kv_heads; p.dim = a.dim; p.vdim = a.vdim; p.window = a.window; p.QT = QT; p.KT = KT; p.kstride = one ? L.kstride_one : L.kstride;
   p.vec = ((size_t)L.Nk * sizeof(T)) % 16 == 0 && ((size_t)L.Nv * sizeof(T)) % 16 == 0;
   // keys are cut over several CTAs per tile when the tiles alone cannot fill the GPU (decoding, short portions)
   const int key_tiles = ceil_div(std::min(a.window, max_ctx) + QT - 1, KT);
   int nsplit = 1;
   if (h->attn_split > 0) nsplit = std::min(h->attn_split, 64);
-  else if (s.count < 148) nsplit = std::min(std::max(296 / std::max(s.count, 1), 1), 64);
+  else if (s.count < 148) nsplit = std::min(std::max((one ? 444 : 296) / std::max(s.count, 1), 1), 64);
   nsplit = std::max(1, std::min(nsplit, key_tiles));
   const int rpt = QT * a.heads;
   while (nsplit > 1 && (size_t)s.count * nsplit * rpt * (a.vdim + 2) > h->part_floats) --nsplit;
@@ -624,7 +631,7 @@ int window_attention(b200_dlm* h, const Layer& L, int n_tok, int max_ctx) {
     else if (L.mma_items == 2) B200_LAUNCH(window_attn_mma_kernel<2>, grid, 256, L.mma_smem, h->stream, p);
     else B200_LAUNCH(window_attn_mma_kernel<4>, grid, 256, L.mma_smem, h->stream, p);
   } else {
-    B200_LAUNCH(window_attn_kernel<T>, dim3(s.count, nsplit), 256, L.attn_smem, h->stream, p);
+    B200_LAUNCH(window_attn_kernel<T>, dim3(s.count, nsplit), 256, one ? L.smem_one : L.attn_smem, h->stream, p);
   }
   B200_TRY(check_launch("window_attn"));
   if (nsplit > 1) {
@@ -647,21 +654,22 @@ int routed_experts(b200_dlm* h, const Layer& L, const T* hb, int n_tok) {
   cudaStream_t st = h->stream;
   B200_TRY(small_proj<T>(h, hb, W, L.router, nullptr, h->route32, n_tok, E, W));
   B200_LAUNCH(moe_route_kernel, ceil_div(n_tok, 4), 128, 0, st, h->route32, E, top, h->moe_idx, h->moe_w, n_tok);
+  bool mma = false;
+  if constexpr (sizeof(T) == 2) mma = h->attn_tc && W % 16 == 0 && F % 16 == 0;
+  const int tile_m = mma ? 128 : 64;
   B200_LAUNCH(moe_group_kernel, 1, 1024, (size_t)2 * E * sizeof(int), st, h->moe_idx, pairs, top, E, h->moe_rank, h->moe_perm, h->moe_row_tok,
-              h->moe_tile_e, h->moe_tile_r0, h->moe_tile_n, h->moe_ntiles);
+              h->moe_tile_e, h->moe_tile_r0, h->moe_tile_n, h->moe_ntiles, tile_m);
   B200_TRY(check_launch("moe route / group"));
-  const int max_tiles = ceil_div(pairs, 64) + std::min(E, pairs);
+  const int max_tiles = ceil_div(pairs, tile_m) + std::min(E, pairs);
   T* act = static_cast<T*>(h->act);
   T* yexp = static_cast<T*>(h->yexp);
   const T* ups = static_cast<const T*>(L.ups);
   const T* downs = static_cast<const T*>(L.downs);
-  bool mma = false;
-  if constexpr (sizeof(T) == 2) mma = h->attn_tc && W % 16 == 0 && F % 16 == 0;
   if (mma) {
     if constexpr (sizeof(T) == 2) {
-      B200_LAUNCH(grouped_gemm_mma_kernel, dim3(ceil_div(F, 64), max_tiles), 128, 0, st, hb, (long long)W, h->moe_row_tok, ups, (long long)W, (long long)F * W,
+      B200_LAUNCH(grouped_gemm_mma_kernel, dim3(ceil_div(F, 128), max_tiles), 256, 0, st, hb, (long long)W, h->moe_row_tok, ups, (long long)W, (long long)F * W,
                   act, (long long)F, (const int*)nullptr, h->moe_tile_e, h->moe_tile_r0, h->moe_tile_n, h->moe_ntiles, F, W, 1);
-      B200_LAUNCH(grouped_gemm_mma_kernel, dim3(ceil_div(W, 64), max_tiles), 128, 0, st, act, (long long)F, (const int*)nullptr, downs, (long long)F, (long long)W * F,
+      B200_LAUNCH(grouped_gemm_mma_kernel, dim3(ceil_div(W, 128), max_tiles), 256, 0, st, act, (long long)F, (const int*)nullptr, downs, (long long)F, (long long)W * F,
                   yexp, (long long)W, h->moe_perm, h->moe_tile_e, h->moe_tile_r0, h->moe_tile_n, h->moe_ntiles, W, F, 0);
     }
   } else {

@@ -755,7 +755,7 @@ __global__ void __launch_bounds__(256) sublayer_end_kernel(float* __restrict__ x
 // ---------------------------------------------------------------------------------------------------------------------------
 // Routed experts.  moe_route_kernel: per token (one warp) the `top` largest router logits (ties: the lower index) and the
 // softmax over those alone.  moe_group_kernel (ONE CTA): sorts the (token, choice) pairs by expert: pos-th row of the grouped
-// order is pair perm[pos] of token row_tok[pos], and cuts every expert's rows into tiles of 64 for the grouped products
+// order is pair perm[pos] of token row_tok[pos], and cuts every expert's rows into tiles of tile_m for the grouped products
 // (tile -> expert, first row, rows); n_tiles[0] = number of tiles.  The order inside an expert follows the atomics and may
 // differ from run to run; a row's result does not depend on it (every row of a product is summed on its own).
 // ---------------------------------------------------------------------------------------------------------------------------
@@ -790,7 +790,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__ idx, int n_pairs, int top, int E, int* __restrict__ rank,
                                                          int* __restrict__ perm, int* __restrict__ row_tok, int* __restrict__ tile_expert,
-                                                         int* __restrict__ tile_row0, int* __restrict__ tile_rows, int* __restrict__ n_tiles) {
+                                                         int* __restrict__ tile_row0, int* __restrict__ tile_rows, int* __restrict__ n_tiles, int tile_m) {
   extern __shared__ int cnt[];          // [E] counts, then [E] offsets
   int* off = cnt + E;
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
@@ -801,7 +801,7 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
     int o = 0, nt = 0;
     for (int e = 0; e < E; ++e) {
       off[e] = o;
-      for (int r0 = 0; r0 < cnt[e]; r0 += 64) { tile_expert[nt] = e; tile_row0[nt] = o + r0; tile_rows[nt] = min(64, cnt[e] - r0); ++nt; }
+      for (int r0 = 0; r0 < cnt[e]; r0 += tile_m) { tile_expert[nt] = e; tile_row0[nt] = o + r0; tile_rows[nt] = min(tile_m, cnt[e] - r0); ++nt; }
       o += cnt[e];
     }
     n_tiles[0] = nt;
@@ -869,69 +869,82 @@ __global__ void __launch_bounds__(256) grouped_gemm_kernel(const TA* __restrict_
 }
 
 // The same grouped product on the tensor cores (mma.sync m16n8k16, bf16 in, fp32 accumulate): K a multiple of 16, rows of A
-// and B on 16-byte boundaries.  CTA tile 64 x 64, 4 warps of 16 rows.
-__global__ void __launch_bounds__(128) grouped_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __restrict__ a_rows,
+// and B on 16-byte boundaries.  CTA tile 128 x 128 (tiles of 128 rows in the tile table), 8 warps of 32 x 64, 32-element
+// k-steps through two shared-memory buffers filled by cp.async (chunks outside M, N or K are zero-filled by a copy of size 0).
+__device__ __forceinline__ void cp_async_16_or_zero(void* smem_dst, const void* src, bool valid) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+
+__global__ void __launch_bounds__(256) grouped_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __restrict__ a_rows,
                                                                const bf16* __restrict__ B, long long ldb, long long sb, bf16* __restrict__ C,
                                                                long long ldc, const int* __restrict__ c_rows, const int* __restrict__ tile_expert,
                                                                const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
                                                                const int* __restrict__ n_tiles, int N, int K, int act) {
-  constexpr int BM = 64, BN = 64, BK = 32, ST = BK + 8;
+  constexpr int BM = 128, BN = 128, BK = 32, ST = BK + 8;
   if ((int)blockIdx.y >= n_tiles[0]) return;
-  __shared__ __align__(16) bf16 As[BM][ST];
-  __shared__ __align__(16) bf16 Bs[BN][ST];
+  __shared__ __align__(16) bf16 As[2][BM][ST];
+  __shared__ __align__(16) bf16 Bs[2][BN][ST];
   __shared__ int arow[BM];
   const int pos0 = tile_row0[blockIdx.y], M = tile_rows[blockIdx.y];
   B += (long long)tile_expert[blockIdx.y] * sb;
   const int n0 = blockIdx.x * BN;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3, mi = lane >> 3;
+  const int wm = (warp & 3) * 32, wn = (warp >> 2) * 64;
   if (threadIdx.x < BM) arow[threadIdx.x] = threadIdx.x < M ? (a_rows ? a_rows[pos0 + threadIdx.x] : pos0 + threadIdx.x) : 0;
   __syncthreads();
-  float acc[8][4];
+  float acc[2][8][4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
-  uint4 ra[2], rb[2];
-  auto fetch = [&](int k0) {
+  for (int a = 0; a < 2; ++a)
+#pragma unroll
+    for (int b = 0; b < 8; ++b) { acc[a][b][0] = acc[a][b][1] = acc[a][b][2] = acc[a][b][3] = 0.f; }
+  auto load = [&](int k0, int buf) {
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
-      const int c = threadIdx.x + 128 * j;
-      const int rr = c / 4, kk = (c % 4) * 8;
-      ra[j] = (rr < M && k0 + kk < K) ? *reinterpret_cast<const uint4*>(A + (long long)arow[rr] * lda + k0 + kk) : make_uint4(0u, 0u, 0u, 0u);
-      rb[j] = (n0 + rr < N && k0 + kk < K) ? *reinterpret_cast<const uint4*>(B + (long long)(n0 + rr) * ldb + k0 + kk) : make_uint4(0u, 0u, 0u, 0u);
+      const int c = threadIdx.x + 256 * j;
+      const int rr = c >> 2, kk = (c & 3) * 8;
+      const bool va = rr < M && k0 + kk < K, vb = n0 + rr < N && k0 + kk < K;
+      cp_async_16_or_zero(&As[buf][rr][kk], va ? A + (long long)arow[rr] * lda + k0 + kk : A, va);
+      cp_async_16_or_zero(&Bs[buf][rr][kk], vb ? B + (long long)(n0 + rr) * ldb + k0 + kk : B, vb);
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  fetch(0);
-  for (int k0 = 0; k0 < K; k0 += BK) {
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int c = threadIdx.x + 128 * j;
-      *reinterpret_cast<uint4*>(&As[c / 4][(c % 4) * 8]) = ra[j];
-      *reinterpret_cast<uint4*>(&Bs[c / 4][(c % 4) * 8]) = rb[j];
-    }
+  load(0, 0);
+  for (int k0 = 0, it = 0; k0 < K; k0 += BK, ++it) {
+    const int buf = it & 1;
+    if (k0 + BK < K) { load(k0 + BK, buf ^ 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+    else asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    if (k0 + BK < K) fetch(k0 + BK);
 #pragma unroll
     for (int ks = 0; ks < BK / 16; ++ks) {
-      unsigned a[4];
-      const int mi = lane >> 3;
-      ldmatrix_x4(a, &As[warp * 16 + (mi & 1) * 8 + (lane & 7)][ks * 16 + (mi >> 1) * 8]);
+      unsigned a[2][4];
+#pragma unroll
+      for (int mf = 0; mf < 2; ++mf) ldmatrix_x4(a[mf], &As[buf][wm + mf * 16 + (mi & 1) * 8 + (lane & 7)][ks * 16 + (mi >> 1) * 8]);
 #pragma unroll
       for (int np = 0; np < 4; ++np) {
         unsigned b[4];
-        ldmatrix_x4(b, &Bs[np * 16 + (mi >> 1) * 8 + (lane & 7)][ks * 16 + (mi & 1) * 8]);
-        mma_bf16_16816(acc[2 * np], a, b[0], b[1]);
-        mma_bf16_16816(acc[2 * np + 1], a, b[2], b[3]);
+        ldmatrix_x4(b, &Bs[buf][wn + np * 16 + (mi >> 1) * 8 + (lane & 7)][ks * 16 + (mi & 1) * 8]);
+#pragma unroll
+        for (int mf = 0; mf < 2; ++mf) {
+          mma_bf16_16816(acc[mf][2 * np], a[mf], b[0], b[1]);
+          mma_bf16_16816(acc[mf][2 * np + 1], a[mf], b[2], b[3]);
+        }
       }
     }
     __syncthreads();
   }
 #pragma unroll
-  for (int nb = 0; nb < 8; ++nb)
+  for (int mf = 0; mf < 2; ++mf)
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
-      const int m = warp * 16 + g + 8 * hf, n = n0 + nb * 8 + 2 * t4;
-      if (m < M) {
-        const long long crow = c_rows ? c_rows[pos0 + m] : pos0 + m;
-        float v0 = acc[nb][2 * hf], v1 = acc[nb][2 * hf + 1];
+      const int m = wm + mf * 16 + g + 8 * hf;
+      if (m >= M) continue;
+      const long long crow = c_rows ? c_rows[pos0 + m] : pos0 + m;
+#pragma unroll
+      for (int nb = 0; nb < 8; ++nb) {
+        const int n = n0 + wn + nb * 8 + 2 * t4;
+        float v0 = acc[mf][nb][2 * hf], v1 = acc[mf][nb][2 * hf + 1];
         if (act) { v0 = fmaxf(v0, 0.f); v0 *= v0; v1 = fmaxf(v1, 0.f); v1 *= v1; }
         if (n < N) C[crow * ldc + n] = __float2bfloat16_rn(v0);
         if (n + 1 < N) C[crow * ldc + n + 1] = __float2bfloat16_rn(v1);
