@@ -93,7 +93,8 @@ struct b200_dlm {
   int last_tokens = 0, last_want = 0;
   int* err = nullptr;
   // sandwich block: step metadata per token (first / last token of its request in the step) and per entry, further buffers
-  int off_first = 0, off_last = 0, off_ent_tok0 = 0, off_ent_ntok = 0, off_ent_slot = 0, off_ent_pos0 = 0, n_entries = 0, max_entry_tokens = 0;
+  int off_first = 0, off_last = 0, off_ent_tok0 = 0, off_ent_ntok = 0, off_ent_slot = 0, off_ent_pos0 = 0, off_ent_par = 0, n_entries = 0, max_entry_tokens = 0;
+  std::vector<char> par;               // per slot: which generation of mLSTM's n and m is current
   float *embw = nullptr, *h32 = nullptr, *qkv32 = nullptr, *scan32 = nullptr, *gate32 = nullptr, *attn32 = nullptr, *route32 = nullptr, *moe_w = nullptr, *scan_prep = nullptr, *scan_v = nullptr;
   void *mixo2 = nullptr, *obuf2 = nullptr, *yexp = nullptr;
   int *moe_idx = nullptr, *moe_rank = nullptr, *moe_perm = nullptr, *moe_row_tok = nullptr, *moe_tile_e = nullptr, *moe_tile_r0 = nullptr,
@@ -566,16 +567,16 @@ int small_proj(b200_dlm* h, const T* x, long long ldx, const void* w, const floa
   return check_launch("small_proj_f32");
 }
 
-template <int MODE, int R>
+template <int MODE, int R, int LPC>
 int launch_scan_r(cudaStream_t st, const ScanParams& p, int n_entries) {
-  const dim3 grid(n_entries * p.heads, ceil_div(p.vdim, 16));
-  const size_t smem = (size_t)2 * p.stage * (p.prow + 16) * 4;
+  const dim3 grid(n_entries * p.heads, ceil_div(p.vdim, 128 / LPC));
+  const size_t smem = (size_t)2 * p.stage * (p.prow + 128 / LPC) * 4;
   static bool attr_set = false;
   if (!attr_set) {
-    B200_CUDA(cudaFuncSetAttribute((matrix_memory_scan_kernel<MODE, R>), cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+    B200_CUDA(cudaFuncSetAttribute((matrix_memory_scan_kernel<MODE, R, LPC>), cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
     attr_set = true;
   }
-  B200_LAUNCH((matrix_memory_scan_kernel<MODE, R>), grid, 128, smem, st, p);
+  B200_LAUNCH((matrix_memory_scan_kernel<MODE, R, LPC>), grid, 128, smem, st, p);
   return check_launch("matrix_memory_scan");
 }
 
@@ -586,12 +587,20 @@ int launch_scan(b200_dlm* h, ScanParams p, int n_tok) {
   p.prep = h->scan_prep; p.vprep = h->scan_v;
   p.vec = p.vdim % 4 == 0;
   p.stage = h->max_entry_tokens <= 8 ? 8 : 16;
+  p.ent_par = h->meta_dev + h->off_ent_par; p.slots = h->slots;
   B200_LAUNCH((scan_prep_kernel<T, MODE>), n_tok, 256, 0, h->stream, p);
   B200_TRY(check_launch("scan_prep"));
-  if (p.dim <= 32) return launch_scan_r<MODE, 4>(h->stream, p, h->n_entries);
-  if (p.dim <= 64) return launch_scan_r<MODE, 8>(h->stream, p, h->n_entries);
-  if (p.dim <= 128) return launch_scan_r<MODE, 16>(h->stream, p, h->n_entries);
-  return launch_scan_r<MODE, 32>(h->stream, p, h->n_entries);
+  // few long requests: 16 lanes per column (twice the CTAs, half the chain per token); batches: 8 lanes per column
+  const bool wide = h->n_entries * p.heads * ceil_div(p.vdim, 16) < 2 * 148 && p.dim > 16;
+  if (wide) {
+    if (p.dim <= 64) return launch_scan_r<MODE, 4, 16>(h->stream, p, h->n_entries);
+    if (p.dim <= 128) return launch_scan_r<MODE, 8, 16>(h->stream, p, h->n_entries);
+    return launch_scan_r<MODE, 16, 16>(h->stream, p, h->n_entries);
+  }
+  if (p.dim <= 32) return launch_scan_r<MODE, 4, 8>(h->stream, p, h->n_entries);
+  if (p.dim <= 64) return launch_scan_r<MODE, 8, 8>(h->stream, p, h->n_entries);
+  if (p.dim <= 128) return launch_scan_r<MODE, 16, 8>(h->stream, p, h->n_entries);
+  return launch_scan_r<MODE, 32, 8>(h->stream, p, h->n_entries);
 }
 
 template <typename T>
@@ -1019,10 +1028,9 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
       max_prep = std::max(max_prep, (size_t)b.heads * (3 * b.dim + 4));
       max_part = std::max(max_part, (size_t)(L.sig_mma >= 0 ? 16 : L.QT) * a.heads * (a.vdim + 2));
     } else {
-      const size_t slices = (size_t)ceil_div(a.vdim, 16);
       B200_TRY(A.alloc_t(&L.St, (size_t)slots * a.heads * a.vdim * a.dim));
-      B200_TRY(A.alloc_t(&L.nvec, (size_t)slots * a.heads * slices * a.dim));
-      B200_TRY(A.alloc_t(&L.mval, (size_t)slots * a.heads * slices));
+      B200_TRY(A.alloc_t(&L.nvec, (size_t)2 * slots * a.heads * a.dim));
+      B200_TRY(A.alloc_t(&L.mval, (size_t)2 * slots * a.heads));
       max_rv = std::max(max_rv, (size_t)a.heads * a.vdim);
       max_gate = std::max(max_gate, (size_t)2 * a.heads);
       max_prep = std::max(max_prep, (size_t)a.heads * (2 * a.dim + 8));
@@ -1090,6 +1098,7 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
   h->off_ent_ntok = off; off += max_entries;
   h->off_ent_slot = off; off += max_entries;
   h->off_ent_pos0 = off; off += max_entries;
+  h->off_ent_par = off; off += max_entries;
   for (auto& s : h->sigs) {
     max_tiles = (size_t)ceil_div64((int64_t)max_step_tokens * s.H, s.rpt) + (size_t)std::min(slots, max_step_tokens);
     s.off_row0 = off; off += (int)max_tiles;
@@ -1102,6 +1111,7 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
   B200_CUDA(cudaEventCreateWithFlags(&h->ev_meta, cudaEventDisableTiming));
   h->slots = slots; h->cap = capacity; h->tmax = max_step_tokens; h->wmax = max_want;
   h->len.assign(slots, 0);
+  h->par.assign(slots, 0);
   h->last_tokens = h->last_want = 0;
   if (!h->f32 && h->use_tc) B200_TRY(tc::prepare_plans(h->plans));
   B200_CUDA(cudaDeviceSynchronize());
@@ -1156,6 +1166,7 @@ int b200_dlm_step(b200_dlm* h, int n_entries, const int32_t* slots_host, const i
       }
     }
     m[h->off_ent_tok0 + e] = t; m[h->off_ent_ntok + e] = n; m[h->off_ent_slot + e] = s; m[h->off_ent_pos0 + e] = base;
+    m[h->off_ent_par + e] = h->par[s];
     const int first = t, lastt = t + n - 1;
     for (int i = 0; i < n; ++i, ++t) {
       m[h->off_tok + t] = tokens_host[t];
@@ -1185,7 +1196,7 @@ int b200_dlm_step(b200_dlm* h, int n_entries, const int32_t* slots_host, const i
     }
     h->ev_used = 0;
   }
-  for (int e = 0; e < n_entries; ++e) h->len[slots_host[e]] += counts_host[e];
+  for (int e = 0; e < n_entries; ++e) { h->len[slots_host[e]] += counts_host[e]; h->par[slots_host[e]] ^= 1; }
   h->last_tokens = t; h->last_want = n_want;
   return B200_OK;
 }

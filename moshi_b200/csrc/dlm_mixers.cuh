@@ -528,8 +528,10 @@ struct ScanParams {
   float* vprep;             // [tokens][heads * vdim] fp32
   int prow;                 // floats per (token, head) row of prep
   float* St;                // [slots][heads][vdim][dim]
-  float* nvec;              // MODE_EXPGATE: [slots][heads][column slices][dim]: every CTA of a head carries its own copy of n and m,
-  float* mval;              // MODE_EXPGATE: [slots][heads][column slices]        so that none reads what another has already replaced
+  float* nvec;              // MODE_EXPGATE: [2][slots][heads][dim]: two generations, so that no CTA of a head reads what another
+  float* mval;              // MODE_EXPGATE: [2][slots][heads]                has already replaced
+  const int* ent_par;       // per entry: the generation to read (the other one is written)
+  int slots;
   const int* ent_tok0;      // per entry: first token of the step, number of tokens, slot, position of the first token
   const int* ent_ntok;
   const int* ent_slot;
@@ -571,50 +573,56 @@ __device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* src, 
   else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
 
-// The recurrence itself.  A CTA owns 16 columns of one (request, head) and walks the request's new tokens in order; lane & 7
-// selects a group of rows (row = group + 8 i), so a column's dot product with q closes with three shuffles.  Tokens arrive in
-// stages of `stage` tokens, copied asynchronously into one of two shared-memory buffers while the other is being consumed.
-// Grid: (entries * heads, ceil(vdim / 16)).
-template <int MODE, int R>      // R rows per thread: dim <= 8 * R
+// The recurrence itself.  A CTA owns 128 / LPC columns of one (request, head) and walks the request's new tokens in order; LPC
+// lanes share a column (row = lane's group + LPC * i, held in registers), so a column's dot product with q closes with
+// log2(LPC) shuffles.  LPC = 8 for batches of requests (few instructions per token, state rows read in full sectors), 16 when a
+// few long requests must fill the GPU (twice the CTAs, half the chain per token).  Tokens arrive in stages of `stage` tokens,
+// copied asynchronously into one of two shared-memory buffers while the other is being consumed.  mLSTM's n and m exist once
+// per (slot, head) in two generations: every CTA reads generation `par` of its entry, the CTA of the first columns writes
+// generation `par ^ 1`.  Grid: (entries * heads, ceil(vdim / (128 / LPC))).
+template <int MODE, int R, int LPC>      // R rows per thread: dim <= LPC * R
 __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
+  constexpr int NC = 128 / LPC;
   const int TT = p.stage;
   extern __shared__ __align__(16) float sm[];
   const int dim = p.dim, vdim = p.vdim, heads = p.heads, prow = p.prow;
-  const int srow = prow + 16;                         // a staged token: its prep row, then its 16 values
+  const int srow = prow + NC;                         // a staged token: its prep row, then its values
   const int ent = blockIdx.x / heads, head = blockIdx.x - ent * heads;
   const int tok0 = p.ent_tok0[ent], nt = p.ent_ntok[ent], slot = p.ent_slot[ent], pos0 = p.ent_pos0[ent];
-  const int rg = threadIdx.x & 7, cl = threadIdx.x >> 3, col = blockIdx.y * 16 + cl;
+  const int rg = threadIdx.x & (LPC - 1), cl = threadIdx.x / LPC, col = blockIdx.y * NC + cl;
   const bool col_ok = col < vdim;
   float* Scol = p.St + (((long long)slot * heads + head) * vdim + (col_ok ? col : 0)) * dim;
-  const long long slice = ((long long)slot * heads + head) * gridDim.y + blockIdx.y;
-  float* nst = MODE == MODE_EXPGATE ? p.nvec + slice * dim : nullptr;
+  const int par = MODE == MODE_EXPGATE ? p.ent_par[ent] : 0;
+  const long long sh = (long long)slot * heads + head;
+  const float* nin = MODE == MODE_EXPGATE ? p.nvec + ((long long)par * p.slots * heads + sh) * dim : nullptr;
+  float* nout = MODE == MODE_EXPGATE ? p.nvec + ((long long)(par ^ 1) * p.slots * heads + sh) * dim : nullptr;
   float S[R], nv[R], m = 0.f;
 #pragma unroll
   for (int i = 0; i < R; ++i) {
-    const int r = rg + 8 * i;
+    const int r = rg + LPC * i;
     const bool live = pos0 > 0 && r < dim;
     S[i] = live && col_ok ? Scol[r] : 0.f;
-    nv[i] = (MODE == MODE_EXPGATE && live) ? nst[r] : 0.f;
+    nv[i] = (MODE == MODE_EXPGATE && live) ? nin[r] : 0.f;
   }
-  if (MODE == MODE_EXPGATE && pos0 > 0) m = p.mval[slice];
+  if (MODE == MODE_EXPGATE && pos0 > 0) m = p.mval[(long long)par * p.slots * heads + sh];
 
   auto issue = [&](int t0, int buf) {
     const int tn = min(TT, nt - t0);
     float* base = sm + buf * TT * srow;
     if (p.vec) {
-      const int pw = prow / 4;
-      for (int i = threadIdx.x; i < tn * (pw + 4); i += 128) {
-        const int tt = i / (pw + 4), e = i - tt * (pw + 4);
+      const int pw = prow / 4, vw = NC / 4;
+      for (int i = threadIdx.x; i < tn * (pw + vw); i += 128) {
+        const int tt = i / (pw + vw), e = i - tt * (pw + vw);
         const long long tok = tok0 + t0 + tt;
         if (e < pw) cp_async_f32(base + tt * srow + e * 4, p.prep + (tok * heads + head) * prow + e * 4, true);
-        else if (blockIdx.y * 16 + (e - pw) * 4 < vdim) cp_async_f32(base + tt * srow + prow + (e - pw) * 4, p.vprep + tok * heads * vdim + head * vdim + blockIdx.y * 16 + (e - pw) * 4, true);
+        else if (blockIdx.y * NC + (e - pw) * 4 < vdim) cp_async_f32(base + tt * srow + prow + (e - pw) * 4, p.vprep + tok * heads * vdim + head * vdim + blockIdx.y * NC + (e - pw) * 4, true);
       }
     } else {
       for (int i = threadIdx.x; i < tn * srow; i += 128) {
         const int tt = i / srow, e = i - tt * srow;
         const long long tok = tok0 + t0 + tt;
         if (e < prow) cp_async_f32(base + tt * srow + e, p.prep + (tok * heads + head) * prow + e, false);
-        else if (blockIdx.y * 16 + (e - prow) < vdim) cp_async_f32(base + tt * srow + e, p.vprep + tok * heads * vdim + head * vdim + blockIdx.y * 16 + (e - prow), false);
+        else if (blockIdx.y * NC + (e - prow) < vdim) cp_async_f32(base + tt * srow + e, p.vprep + tok * heads * vdim + head * vdim + blockIdx.y * NC + (e - prow), false);
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -627,7 +635,7 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
     else asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     const float* base = sm + (st & 1) * TT * srow;
-#pragma unroll 4
+#pragma unroll 2
     for (int tt = 0; tt < tn; ++tt) {
       const float* qq = base + tt * srow;
       const float* kk = qq + dim;
@@ -643,7 +651,7 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
       }
 #pragma unroll
       for (int i = 0; i < R; ++i) {
-        const int r = rg + 8 * i;
+        const int r = rg + LPC * i;
         if (r < dim) {
           const float kv = kk[r], qv = qq[r];
           if (MODE == MODE_DECAY) {
@@ -657,13 +665,11 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
         }
       }
       acc += acc1;
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+#pragma unroll
+      for (int o = 1; o < LPC; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (MODE == MODE_EXPGATE) {
-        nq += __shfl_xor_sync(0xffffffffu, nq, 1);
-        nq += __shfl_xor_sync(0xffffffffu, nq, 2);
-        nq += __shfl_xor_sync(0xffffffffu, nq, 4);
+#pragma unroll
+        for (int o = 1; o < LPC; o <<= 1) nq += __shfl_xor_sync(0xffffffffu, nq, o);
         acc = acc / (fmaxf(fabsf(nq), expf(-m2)) + 1e-6f);
       }
       if (rg == 0 && col_ok) p.out[(long long)(tok0 + t0 + tt) * heads * vdim + head * vdim + col] = acc;
@@ -672,13 +678,13 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
   }
 #pragma unroll
   for (int i = 0; i < R; ++i) {
-    const int r = rg + 8 * i;
+    const int r = rg + LPC * i;
     if (r < dim) {
       if (col_ok) Scol[r] = S[i];
-      if (MODE == MODE_EXPGATE && cl == 0) nst[r] = nv[i];
+      if (MODE == MODE_EXPGATE && blockIdx.y == 0 && cl == 0) nout[r] = nv[i];
     }
   }
-  if (MODE == MODE_EXPGATE && threadIdx.x == 0) p.mval[slice] = m;
+  if (MODE == MODE_EXPGATE && blockIdx.y == 0 && threadIdx.x == 0) p.mval[(long long)(par ^ 1) * p.slots * heads + sh] = m;
 }
 
 // what leaves a recurrent mixer: per head rms_norm over vdim (weight w[h * wstride + c]: wstride = 0 shares one row between
