@@ -676,9 +676,14 @@ int routed_experts(b200_dlm* h, const Layer& L, const T* hb, int n_tok) {
   const T* downs = static_cast<const T*>(L.downs);
   if (mma) {
     if constexpr (sizeof(T) == 2) {
-      B200_LAUNCH(grouped_gemm_mma_kernel, dim3(ceil_div(F, 128), max_tiles), 256, 0, st, hb, (long long)W, h->moe_row_tok, ups, (long long)W, (long long)F * W,
+      static bool attr_set = false;
+      if (!attr_set) {
+        B200_CUDA(cudaFuncSetAttribute(grouped_gemm_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GG_SMEM));
+        attr_set = true;
+      }
+      B200_LAUNCH(grouped_gemm_mma_kernel, dim3(ceil_div(F, 128), max_tiles), 256, GG_SMEM, st, hb, (long long)W, h->moe_row_tok, ups, (long long)W, (long long)F * W,
                   act, (long long)F, (const int*)nullptr, h->moe_tile_e, h->moe_tile_r0, h->moe_tile_n, h->moe_ntiles, F, W, 1);
-      B200_LAUNCH(grouped_gemm_mma_kernel, dim3(ceil_div(W, 128), max_tiles), 256, 0, st, act, (long long)F, (const int*)nullptr, downs, (long long)F, (long long)W * F,
+      B200_LAUNCH(grouped_gemm_mma_kernel, dim3(ceil_div(W, 128), max_tiles), 256, GG_SMEM, st, act, (long long)F, (const int*)nullptr, downs, (long long)F, (long long)W * F,
                   yexp, (long long)W, h->moe_perm, h->moe_tile_e, h->moe_tile_r0, h->moe_tile_n, h->moe_ntiles, W, F, 0);
     }
   } else {

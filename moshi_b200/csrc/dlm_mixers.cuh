@@ -875,7 +875,7 @@ __global__ void __launch_bounds__(256) grouped_gemm_kernel(const TA* __restrict_
 }
 
 // The same grouped product on the tensor cores (mma.sync m16n8k16, bf16 in, fp32 accumulate): K a multiple of 16, rows of A
-// and B on 16-byte boundaries.  CTA tile 128 x 128 (tiles of 128 rows in the tile table), 8 warps of 32 x 64, 32-element
+// and B on 16-byte boundaries.  CTA tile 128 x 128 (tiles of 128 rows in the tile table), 8 warps of 32 x 64, 64-element
 // k-steps through two shared-memory buffers filled by cp.async (chunks outside M, N or K are zero-filled by a copy of size 0).
 __device__ __forceinline__ void cp_async_16_or_zero(void* smem_dst, const void* src, bool valid) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -883,16 +883,20 @@ __device__ __forceinline__ void cp_async_16_or_zero(void* smem_dst, const void* 
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
 }
 
-__global__ void __launch_bounds__(256) grouped_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __restrict__ a_rows,
-                                                               const bf16* __restrict__ B, long long ldb, long long sb, bf16* __restrict__ C,
-                                                               long long ldc, const int* __restrict__ c_rows, const int* __restrict__ tile_expert,
-                                                               const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
-                                                               const int* __restrict__ n_tiles, int N, int K, int act) {
-  constexpr int BM = 128, BN = 128, BK = 32, ST = BK + 8;
+constexpr int GG_BM = 128, GG_BN = 128, GG_BK = 64, GG_ST = GG_BK + 8;
+constexpr size_t GG_SMEM = (size_t)2 * (GG_BM + GG_BN) * GG_ST * 2 + GG_BM * 4;
+
+__global__ void __launch_bounds__(256, 2) grouped_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __restrict__ a_rows,
+                                                                  const bf16* __restrict__ B, long long ldb, long long sb, bf16* __restrict__ C,
+                                                                  long long ldc, const int* __restrict__ c_rows, const int* __restrict__ tile_expert,
+                                                                  const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
+                                                                  const int* __restrict__ n_tiles, int N, int K, int act) {
+  constexpr int BM = GG_BM, BN = GG_BN, BK = GG_BK, ST = GG_ST;
   if ((int)blockIdx.y >= n_tiles[0]) return;
-  __shared__ __align__(16) bf16 As[2][BM][ST];
-  __shared__ __align__(16) bf16 Bs[2][BN][ST];
-  __shared__ int arow[BM];
+  extern __shared__ __align__(16) unsigned char gg_smem[];
+  bf16 (*As)[BM][ST] = reinterpret_cast<bf16 (*)[BM][ST]>(gg_smem);                                  // [2][BM][ST]
+  bf16 (*Bs)[BN][ST] = reinterpret_cast<bf16 (*)[BN][ST]>(gg_smem + (size_t)2 * BM * ST * 2);        // [2][BN][ST]
+  int* arow = reinterpret_cast<int*>(gg_smem + (size_t)2 * (BM + BN) * ST * 2);
   const int pos0 = tile_row0[blockIdx.y], M = tile_rows[blockIdx.y];
   B += (long long)tile_expert[blockIdx.y] * sb;
   const int n0 = blockIdx.x * BN;
@@ -907,9 +911,9 @@ __global__ void __launch_bounds__(256) grouped_gemm_mma_kernel(const bf16* __res
     for (int b = 0; b < 8; ++b) { acc[a][b][0] = acc[a][b][1] = acc[a][b][2] = acc[a][b][3] = 0.f; }
   auto load = [&](int k0, int buf) {
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < 4; ++j) {
       const int c = threadIdx.x + 256 * j;
-      const int rr = c >> 2, kk = (c & 3) * 8;
+      const int rr = c >> 3, kk = (c & 7) * 8;
       const bool va = rr < M && k0 + kk < K, vb = n0 + rr < N && k0 + kk < K;
       cp_async_16_or_zero(&As[buf][rr][kk], va ? A + (long long)arow[rr] * lda + k0 + kk : A, va);
       cp_async_16_or_zero(&Bs[buf][rr][kk], vb ? B + (long long)(n0 + rr) * ldb + k0 + kk : B, vb);
@@ -940,6 +944,7 @@ __global__ void __launch_bounds__(256) grouped_gemm_mma_kernel(const bf16* __res
     }
     __syncthreads();
   }
+  const bool pair_ok = (ldc & 1) == 0 && (reinterpret_cast<uintptr_t>(C) & 3) == 0;      // two columns in one 4-byte store
 #pragma unroll
   for (int mf = 0; mf < 2; ++mf)
 #pragma unroll
@@ -952,8 +957,12 @@ __global__ void __launch_bounds__(256) grouped_gemm_mma_kernel(const bf16* __res
         const int n = n0 + wn + nb * 8 + 2 * t4;
         float v0 = acc[mf][nb][2 * hf], v1 = acc[mf][nb][2 * hf + 1];
         if (act) { v0 = fmaxf(v0, 0.f); v0 *= v0; v1 = fmaxf(v1, 0.f); v1 *= v1; }
-        if (n < N) C[crow * ldc + n] = __float2bfloat16_rn(v0);
-        if (n + 1 < N) C[crow * ldc + n + 1] = __float2bfloat16_rn(v1);
+        if (n + 1 < N && pair_ok) {
+          *reinterpret_cast<unsigned*>(C + crow * ldc + n) = pack_bf16(v0, v1);
+        } else {
+          if (n < N) C[crow * ldc + n] = __float2bfloat16_rn(v0);
+          if (n + 1 < N) C[crow * ldc + n + 1] = __float2bfloat16_rn(v1);
+        }
       }
     }
 }
