@@ -567,16 +567,17 @@ int small_proj(b200_dlm* h, const T* x, long long ldx, const void* w, const floa
   return check_launch("small_proj_f32");
 }
 
-template <int MODE, int R, int LPC>
+template <int MODE, int R, int LPC, int CB>
 int launch_scan_r(cudaStream_t st, const ScanParams& p, int n_entries) {
-  const dim3 grid(n_entries * p.heads, ceil_div(p.vdim, 128 / LPC));
-  const size_t smem = (size_t)2 * p.stage * (p.prow + 128 / LPC) * 4;
+  constexpr int NC = 128 / LPC * CB;
+  const dim3 grid(n_entries * p.heads, ceil_div(p.vdim, NC));
+  const size_t smem = (size_t)2 * p.stage * (p.prow + NC) * 4;
   static bool attr_set = false;
   if (!attr_set) {
-    B200_CUDA(cudaFuncSetAttribute((matrix_memory_scan_kernel<MODE, R, LPC>), cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+    B200_CUDA(cudaFuncSetAttribute((matrix_memory_scan_kernel<MODE, R, LPC, CB>), cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
     attr_set = true;
   }
-  B200_LAUNCH((matrix_memory_scan_kernel<MODE, R, LPC>), grid, 128, smem, st, p);
+  B200_LAUNCH((matrix_memory_scan_kernel<MODE, R, LPC, CB>), grid, 128, smem, st, p);
   return check_launch("matrix_memory_scan");
 }
 
@@ -590,17 +591,19 @@ int launch_scan(b200_dlm* h, ScanParams p, int n_tok) {
   p.ent_par = h->meta_dev + h->off_ent_par; p.slots = h->slots;
   B200_LAUNCH((scan_prep_kernel<T, MODE>), n_tok, 256, 0, h->stream, p);
   B200_TRY(check_launch("scan_prep"));
-  // few long requests: 16 lanes per column (twice the CTAs, half the chain per token); batches: 8 lanes per column
-  const bool wide = h->n_entries * p.heads * ceil_div(p.vdim, 16) < 2 * 148 && p.dim > 16;
+  // a few long requests: 16 lanes per column (twice the CTAs, half the chain per token); batches and single tokens: 8 lanes per
+  // column (state rows read in full sectors).  Measured on 2048-token prompts, 8 heads of 128 x 256: 8 / 16 / 32 lanes per
+  // column 0.90 / 0.82 / 0.98 ms per layer; 16 lanes sharing 2 columns per thread 1.22 ms (fewer warps to overlap the chains).
+  const bool wide = h->max_entry_tokens > 8 && h->n_entries * p.heads * ceil_div(p.vdim, 16) < 2 * 148 && p.dim > 16;
   if (wide) {
-    if (p.dim <= 64) return launch_scan_r<MODE, 4, 16>(h->stream, p, h->n_entries);
-    if (p.dim <= 128) return launch_scan_r<MODE, 8, 16>(h->stream, p, h->n_entries);
-    return launch_scan_r<MODE, 16, 16>(h->stream, p, h->n_entries);
+    if (p.dim <= 64) return launch_scan_r<MODE, 4, 16, 1>(h->stream, p, h->n_entries);
+    if (p.dim <= 128) return launch_scan_r<MODE, 8, 16, 1>(h->stream, p, h->n_entries);
+    return launch_scan_r<MODE, 16, 16, 1>(h->stream, p, h->n_entries);
   }
-  if (p.dim <= 32) return launch_scan_r<MODE, 4, 8>(h->stream, p, h->n_entries);
-  if (p.dim <= 64) return launch_scan_r<MODE, 8, 8>(h->stream, p, h->n_entries);
-  if (p.dim <= 128) return launch_scan_r<MODE, 16, 8>(h->stream, p, h->n_entries);
-  return launch_scan_r<MODE, 32, 8>(h->stream, p, h->n_entries);
+  if (p.dim <= 32) return launch_scan_r<MODE, 4, 8, 1>(h->stream, p, h->n_entries);
+  if (p.dim <= 64) return launch_scan_r<MODE, 8, 8, 1>(h->stream, p, h->n_entries);
+  if (p.dim <= 128) return launch_scan_r<MODE, 16, 8, 1>(h->stream, p, h->n_entries);
+  return launch_scan_r<MODE, 32, 8, 1>(h->stream, p, h->n_entries);
 }
 
 template <typename T>

@@ -573,35 +573,37 @@ __device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* src, 
   else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
 
-// The recurrence itself.  A CTA owns 128 / LPC columns of one (request, head) and walks the request's new tokens in order; LPC
-// lanes share a column (row = lane's group + LPC * i, held in registers), so a column's dot product with q closes with
-// log2(LPC) shuffles.  LPC = 8 for batches of requests (few instructions per token, state rows read in full sectors), 16 when a
-// few long requests must fill the GPU (twice the CTAs, half the chain per token).  Tokens arrive in stages of `stage` tokens,
+// The recurrence itself.  A CTA owns 128 / LPC * CB columns of one (request, head) and walks the request's new tokens in order;
+// LPC lanes share CB adjacent columns (row = lane's group + LPC * i, held in registers), so a column's dot product with q closes
+// with log2(LPC) shuffles, and every q, k and decay element a thread reads from shared memory serves CB columns.  Batches of
+// requests: LPC = 8 (many CTAs, state rows read in full sectors); a few long requests: LPC = 16 (twice the CTAs, half the chain
+// per token).  CB = 1 is what runs: the kernel is bound by the chain from token to token, and more columns per thread mean
+// fewer warps to overlap it.  Tokens arrive in stages of `stage` tokens,
 // copied asynchronously into one of two shared-memory buffers while the other is being consumed.  mLSTM's n and m exist once
 // per (slot, head) in two generations: every CTA reads generation `par` of its entry, the CTA of the first columns writes
-// generation `par ^ 1`.  Grid: (entries * heads, ceil(vdim / (128 / LPC))).
-template <int MODE, int R, int LPC>      // R rows per thread: dim <= LPC * R
+// generation `par ^ 1`.  Grid: (entries * heads, ceil(vdim / (128 / LPC * CB))).
+template <int MODE, int R, int LPC, int CB>      // R rows per thread (dim <= LPC * R), CB adjacent columns per thread
 __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
-  constexpr int NC = 128 / LPC;
+  constexpr int NC = 128 / LPC * CB;                  // columns per CTA
   const int TT = p.stage;
   extern __shared__ __align__(16) float sm[];
   const int dim = p.dim, vdim = p.vdim, heads = p.heads, prow = p.prow;
   const int srow = prow + NC;                         // a staged token: its prep row, then its values
   const int ent = blockIdx.x / heads, head = blockIdx.x - ent * heads;
   const int tok0 = p.ent_tok0[ent], nt = p.ent_ntok[ent], slot = p.ent_slot[ent], pos0 = p.ent_pos0[ent];
-  const int rg = threadIdx.x & (LPC - 1), cl = threadIdx.x / LPC, col = blockIdx.y * NC + cl;
-  const bool col_ok = col < vdim;
-  float* Scol = p.St + (((long long)slot * heads + head) * vdim + (col_ok ? col : 0)) * dim;
+  const int rg = threadIdx.x & (LPC - 1), cl = threadIdx.x / LPC * CB, col = blockIdx.y * NC + cl;      // first of the thread's columns
+  float* Sbase = p.St + ((long long)slot * heads + head) * vdim * dim;
   const int par = MODE == MODE_EXPGATE ? p.ent_par[ent] : 0;
   const long long sh = (long long)slot * heads + head;
   const float* nin = MODE == MODE_EXPGATE ? p.nvec + ((long long)par * p.slots * heads + sh) * dim : nullptr;
   float* nout = MODE == MODE_EXPGATE ? p.nvec + ((long long)(par ^ 1) * p.slots * heads + sh) * dim : nullptr;
-  float S[R], nv[R], m = 0.f;
+  float S[R][CB], nv[R], m = 0.f;
 #pragma unroll
   for (int i = 0; i < R; ++i) {
     const int r = rg + LPC * i;
     const bool live = pos0 > 0 && r < dim;
-    S[i] = live && col_ok ? Scol[r] : 0.f;
+#pragma unroll
+    for (int j = 0; j < CB; ++j) S[i][j] = live && col + j < vdim ? Sbase[(long long)(col + j) * dim + r] : 0.f;
     nv[i] = (MODE == MODE_EXPGATE && live) ? nin[r] : 0.f;
   }
   if (MODE == MODE_EXPGATE && pos0 > 0) m = p.mval[(long long)par * p.slots * heads + sh];
@@ -640,8 +642,9 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
       const float* qq = base + tt * srow;
       const float* kk = qq + dim;
       const float* aa = kk + dim;
-      const float v = col_ok ? qq[prow + cl] : 0.f;
-      float acc = 0.f, acc1 = 0.f, nq = 0.f, fa = 1.f, fb = 1.f, m2 = 0.f;
+      float v[CB], acc[CB], nq = 0.f, fa = 1.f, fb = 1.f, m2 = 0.f;
+#pragma unroll
+      for (int j = 0; j < CB; ++j) { v[j] = col + j < vdim ? qq[prow + cl + j] : 0.f; acc[j] = 0.f; }
       if (MODE == MODE_EXPGATE) {
         const float il = aa[0], fl = aa[1];
         m2 = fmaxf(fl + m, il);
@@ -653,26 +656,35 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
       for (int i = 0; i < R; ++i) {
         const int r = rg + LPC * i;
         if (r < dim) {
-          const float kv = kk[r], qv = qq[r];
-          if (MODE == MODE_DECAY) {
-            S[i] = fmaf(aa[r], S[i], kv * v);
-          } else {
-            S[i] = fmaf(fa, S[i], fb * kv * v);
-            nv[i] = fmaf(fa, nv[i], fb * kv);
+          const float kv = kk[r] * fb, qv = qq[r];
+          const float ar = MODE == MODE_DECAY ? aa[r] : fa;
+#pragma unroll
+          for (int j = 0; j < CB; ++j) {
+            S[i][j] = fmaf(ar, S[i][j], kv * v[j]);
+            acc[j] = fmaf(S[i][j], qv, acc[j]);
+          }
+          if (MODE == MODE_EXPGATE) {
+            nv[i] = fmaf(fa, nv[i], kv);
             nq = fmaf(nv[i], qv, nq);
           }
-          if (i & 1) acc1 = fmaf(S[i], qv, acc1); else acc = fmaf(S[i], qv, acc);
         }
       }
-      acc += acc1;
 #pragma unroll
-      for (int o = 1; o < LPC; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      for (int j = 0; j < CB; ++j)
+#pragma unroll
+        for (int o = 1; o < LPC; o <<= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
       if (MODE == MODE_EXPGATE) {
 #pragma unroll
         for (int o = 1; o < LPC; o <<= 1) nq += __shfl_xor_sync(0xffffffffu, nq, o);
-        acc = acc / (fmaxf(fabsf(nq), expf(-m2)) + 1e-6f);
+        const float den = 1.f / (fmaxf(fabsf(nq), expf(-m2)) + 1e-6f);
+#pragma unroll
+        for (int j = 0; j < CB; ++j) acc[j] *= den;
       }
-      if (rg == 0 && col_ok) p.out[(long long)(tok0 + t0 + tt) * heads * vdim + head * vdim + col] = acc;
+      if (rg == 0) {
+        float* o = p.out + (long long)(tok0 + t0 + tt) * heads * vdim + head * vdim + col;
+#pragma unroll
+        for (int j = 0; j < CB; ++j) if (col + j < vdim) o[j] = acc[j];
+      }
     }
     __syncthreads();
   }
@@ -680,7 +692,8 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
   for (int i = 0; i < R; ++i) {
     const int r = rg + LPC * i;
     if (r < dim) {
-      if (col_ok) Scol[r] = S[i];
+#pragma unroll
+      for (int j = 0; j < CB; ++j) if (col + j < vdim) Sbase[(long long)(col + j) * dim + r] = S[i][j];
       if (MODE == MODE_EXPGATE && blockIdx.y == 0 && cl == 0) nout[r] = nv[i];
     }
   }
