@@ -395,18 +395,22 @@ typedef struct {
 } b200_dlm_config;
 
 int b200_dlm_create(const b200_dlm_config* cfg, b200_dlm** out);
-/* Tensors under the checkpoint's names ("embed", "l<i>.norm1", "l<i>.mix.q", ..., "final.norm", "head"), bf16 or f32. */
+/* Tensors under the checkpoint's names ("embed", "l<i>.norm1", "l<i>.mix.q", "l<i>.mix.left.q.conv", "l<i>.mlp.e<k>.up", ...,
+ * "final.norm", "head"), bf16 or f32.  Sizes that the configuration does not carry are read from the shapes (the rank of the
+ * decay's bottleneck from "l<i>.mix.right.a1"). */
 int b200_dlm_load_tensor(b200_dlm* h, const char* name, const void* data_dev, int dtype, int ndim, const int64_t* shape);
 int b200_dlm_finalize(b200_dlm* h);
 int b200_dlm_destroy(b200_dlm* h);
-/* Allocates the latent cache ([slots][capacity][kv_rank] per layer) and the step buffers (up to max_step_tokens new tokens
- * and max_want logit rows per step). */
+/* Allocates what a slot holds per layer (latents [slots][capacity][kv_rank]; or keys and values of `capacity` tokens, the
+ * carried inputs of the causal convolutions and the matrix memories of the recurrent mixers) and the step buffers (up to
+ * max_step_tokens new tokens and max_want logit rows per step). */
 int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_tokens, int max_want, void* stream);
 int b200_dlm_cache_end(b200_dlm* h);
 int b200_dlm_set_stream(b200_dlm* h, void* stream);
 /* "use_tc" (before finalize; 1 = bf16 linears of eligible shapes on the LM's tcgen05 GEMM), "trace_layers" (before cache_begin),
- * "attn_split" (CTAs per attention tile along the keys; 0 = chosen per step), "attn_tc" (0: latent attention on the CUDA
- * cores also where the tensor-core kernel would take it), "time_kernels" (CUDA events around every
+ * "attn_split" (CTAs per attention tile along the keys; 0 = chosen per step), "attn_tc" (0: attention and grouped expert
+ * products on the CUDA cores also where a tensor-core kernel would take them; 2: the tensor-core window attention also for
+ * single-token requests), "time_kernels" (CUDA events around every
  * operation, summed per class: a step then waits for its own end). */
 int b200_dlm_set_option(b200_dlm* h, const char* name, int value);
 /* Milliseconds spent so far per class of operation under "time_kernels": [0] linears, [1] attention, [2] the small products

@@ -504,7 +504,7 @@ int finalize_sandwich_layer(b200_dlm* h, int i, std::vector<void*>& drop) {
     }
     if (!h->f32 && a.dim % 16 == 0 && a.vdim % 16 == 0) {     // bf16 cache, fragment-sized heads: the tensor-core kernel, if it fits
       const size_t Hh = a.heads, QS = L.Nq + 8, KS = L.Nk + 8, VS = L.Nv + 8;
-      const size_t sm = 2 * (16 * QS + 32 * KS + 32 * VS + Hh * 16 * 40) + 4 * (Hh * 16 * 40 + Hh * Hh + 3 * Hh * 16);
+      const size_t sm = 2 * (16 * QS + 32 * KS + 32 * VS + Hh * 16 * 40) + 4 * (Hh * 16 * 40 + Hh * std::max<size_t>(Hh, 16) + 3 * Hh * 16);
       const int items = ceil_div(a.heads * ceil_div(a.vdim, 64), 8);
       if (sm <= 220 * 1024 && items <= 4) { L.sig_mma = add_sig(h, a.heads, 16 * a.heads); L.mma_items = items <= 2 ? items : 4; L.mma_smem = sm; }
     }

@@ -323,8 +323,8 @@ __global__ void __launch_bounds__(256) window_attn_mma_kernel(WindowAttnParams p
   bf16* Vs = Ks + KT * KS;                                        // [32][VS]
   bf16* pb = Vs + KT * VS;                                        // [H][16][PS] softmax weights of the key tile
   float* sraw = reinterpret_cast<float*>(pb + H * QT * PS);       // [H][16][SS] raw scores
-  float* mixs = sraw + H * QT * SS;                               // [H][H]
-  float* rm = mixs + H * H;                                       // [H * 16] running maximum, row = h * 16 + token
+  float* mixs = sraw + H * QT * SS;                               // [H][max(H, 16)]
+  float* rm = mixs + H * max(H, 16);                              // [H * 16] running maximum, row = h * 16 + token
   float* rl = rm + H * QT;
   float* rc = rl + H * QT;
   const int tile = blockIdx.x, split = blockIdx.y;
@@ -344,7 +344,11 @@ __global__ void __launch_bounds__(256) window_attn_mma_kernel(WindowAttnParams p
     if (qt < nt) v = *reinterpret_cast<const float2*>(p.q + (long long)(tok0 + qt) * p.ldq + e);
     *reinterpret_cast<unsigned*>(Qs + qt * QS + e) = pack_bf16(v.x, v.y);
   }
-  for (int i = threadIdx.x; i < H * H; i += 256) mixs[i] = p.mix[i];
+  if (H <= 16) {      // rows padded to 16 entries (zeros) for the register-blocked mix
+    for (int i = threadIdx.x; i < H * 16; i += 256) mixs[i] = (i & 15) < H ? p.mix[(i >> 4) * H + (i & 15)] : 0.f;
+  } else {
+    for (int i = threadIdx.x; i < H * H; i += 256) mixs[i] = p.mix[i];
+  }
   for (int i = threadIdx.x; i < H * QT; i += 256) {
     if (split == 0) { rm[i] = p.sink[i / QT]; rl[i] = 1.f; }
     else { rm[i] = -INFINITY; rl[i] = 0.f; }
@@ -401,24 +405,56 @@ __global__ void __launch_bounds__(256) window_attn_mma_kernel(WindowAttnParams p
       }
     }
     __syncthreads();
-    // (2) mix over heads, mask, online softmax; lane = key
-    for (int row = warp; row < H * QT; row += 8) {
-      const int h = row / QT, qt = row - h * QT;
-      const int pos = p0 + qt, kj = kb + lane;
-      float s = -INFINITY;
-      if (lane < nk && qt < nt && kj <= pos && pos - kj < p.window) {
-        s = 0.f;
-        for (int g = 0; g < H; ++g) s = fmaf(mixs[h * H + g], sraw[(g * QT + qt) * SS + lane], s);
+    // (2) mix over heads, mask, online softmax; lane = key.  Up to 16 heads: a warp takes a token, keeps the token's raw scores
+    // of all heads in registers and reads each row of the mix matrix (padded to 16) as four 16-byte broadcasts.
+    if (H <= 16) {
+      for (int qt = warp; qt < QT; qt += 8) {
+        const int pos = p0 + qt, kj = kb + lane;
+        const bool vis = lane < nk && qt < nt && kj <= pos && pos - kj < p.window;
+        float raw[16];
+#pragma unroll
+        for (int g = 0; g < 16; ++g) raw[g] = g < H ? sraw[(g * QT + qt) * SS + lane] : 0.f;
+        for (int h = 0; h < H; ++h) {
+          const float4* mr = reinterpret_cast<const float4*>(mixs + h * 16);
+          float s = 0.f;
+#pragma unroll
+          for (int g4 = 0; g4 < 4; ++g4) {
+            const float4 mv = mr[g4];
+            s = fmaf(mv.x, raw[4 * g4], s); s = fmaf(mv.y, raw[4 * g4 + 1], s); s = fmaf(mv.z, raw[4 * g4 + 2], s); s = fmaf(mv.w, raw[4 * g4 + 3], s);
+          }
+          if (!vis) s = -INFINITY;
+          const int row = h * QT + qt;
+          const float mo = rm[row], mn = fmaxf(mo, warp_max(s));
+          const float w = s > -INFINITY ? expf(s - mn) : 0.f;
+          const float sum = warp_sum(w);
+          pb[row * PS + lane] = __float2bfloat16_rn(w);
+          if (lane == 0) {
+            const float corr = mn > -INFINITY ? expf(mo - mn) : 1.f;
+            rc[row] = corr;
+            rl[row] = rl[row] * corr + sum;
+            rm[row] = mn;
+          }
+        }
       }
-      const float mo = rm[row], mn = fmaxf(mo, warp_max(s));
-      const float w = s > -INFINITY ? expf(s - mn) : 0.f;
-      const float sum = warp_sum(w);
-      pb[row * PS + lane] = __float2bfloat16_rn(w);
-      if (lane == 0) {
-        const float corr = mn > -INFINITY ? expf(mo - mn) : 1.f;
-        rc[row] = corr;
-        rl[row] = rl[row] * corr + sum;
-        rm[row] = mn;
+    } else {
+      for (int row = warp; row < H * QT; row += 8) {
+        const int h = row / QT, qt = row - h * QT;
+        const int pos = p0 + qt, kj = kb + lane;
+        float s = -INFINITY;
+        if (lane < nk && qt < nt && kj <= pos && pos - kj < p.window) {
+          s = 0.f;
+          for (int g = 0; g < H; ++g) s = fmaf(mixs[h * H + g], sraw[(g * QT + qt) * SS + lane], s);
+        }
+        const float mo = rm[row], mn = fmaxf(mo, warp_max(s));
+        const float w = s > -INFINITY ? expf(s - mn) : 0.f;
+        const float sum = warp_sum(w);
+        pb[row * PS + lane] = __float2bfloat16_rn(w);
+        if (lane == 0) {
+          const float corr = mn > -INFINITY ? expf(mo - mn) : 1.f;
+          rc[row] = corr;
+          rl[row] = rl[row] * corr + sum;
+          rm[row] = mn;
+        }
       }
     }
     __syncthreads();
