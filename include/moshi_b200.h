@@ -368,7 +368,7 @@ typedef struct {
   int kv_heads;               /* window attention: key/value heads (query head h uses h / (heads / kv_heads)) */
   int kv_rank;                /* latent attention: size of the cached latent                    */
   float scale;                /* multiplies q.k                                                 */
-  int window;                 /* window attention: a token sees itself and window - 1 before it */
+  int window;                 /* window attention: position p attends to keys j with 0 <= p - j < window */
   int conv_taps;              /* window attention: taps of the convolution on q, k, v (<= 1: none) */
   int rot_dims;               /* rotated dimensions per head (even, <= dim)                     */
   float rot_base, rot_factor, rot_low, rot_high, rot_original;   /* rot_factor <= 0: frequencies as they are */

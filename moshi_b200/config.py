@@ -278,7 +278,7 @@ BLOCKS = {"gated_depth_average": 0, "sandwich": 1}                              
 class MixerConfig:
     """One token mixer with its sizes and constants (the fields a kind does not use stay 0).
 
-    ``window_attention``: ``kv_heads`` key/value heads, a token sees itself and the ``window - 1`` tokens before it, a causal
+    ``window_attention``: ``kv_heads`` key/value heads, position p attends to keys j with 0 <= p - j < ``window``, a causal
     convolution of ``conv`` taps on the projected q / k / v, rotary positions on the first ``rot_dims`` dimensions of a head with
     base ``rot_base`` and (optionally) wavelength-dependent rescaling ``rot_scaling`` = {factor, low, high, original}.
     ``gla``: per-channel decay sigmoid(z)^(1 / tau), z through a bottleneck of ``decay_rank`` (a tensor's shape, not a config key).
