@@ -95,6 +95,11 @@ struct b200_dlm {
   // sandwich block: step metadata per token (first / last token of its request in the step) and per entry, further buffers
   int off_first = 0, off_last = 0, off_ent_tok0 = 0, off_ent_ntok = 0, off_ent_slot = 0, off_ent_pos0 = 0, off_ent_par = 0, n_entries = 0, max_entry_tokens = 0;
   std::vector<char> par;               // per slot: which generation of mLSTM's n and m is current
+  // recurrences: portions of at least 2 * scan_seg tokens run as segments of scan_seg tokens side by side (units = entries after the cut)
+  int scan_seg = 256, n_units = 0, max_seg_units = 0, off_ent_seg = 0, off_ent_nseg = 0, off_ent_buf = 0;
+  struct ScanUnit { int tok0, ntok, seg, buf; };
+  std::vector<ScanUnit> units;
+  float *segS = nullptr, *segB = nullptr, *segM = nullptr, *tokM = nullptr, *corr = nullptr;
   float *embw = nullptr, *h32 = nullptr, *qkv32 = nullptr, *scan32 = nullptr, *gate32 = nullptr, *attn32 = nullptr, *route32 = nullptr, *moe_w = nullptr, *scan_prep = nullptr, *scan_v = nullptr;
   void *mixo2 = nullptr, *obuf2 = nullptr, *yexp = nullptr;
   int *moe_idx = nullptr, *moe_rank = nullptr, *moe_perm = nullptr, *moe_row_tok = nullptr, *moe_tile_e = nullptr, *moe_tile_r0 = nullptr,
@@ -161,9 +166,9 @@ int seal_weight(b200_dlm* h, Weight& w, void* rm, int N, int K, std::vector<void
 
 template <typename TA, typename TB, typename TC>
 int gemm_nt(cudaStream_t st, const TA* A, long long lda, long long sa, const TB* B, long long ldb, long long sb, TC* C, long long ldc,
-            long long sc, int M, int N, int K, int batch, float alpha) {
+            long long sc, int M, int N, int K, int batch, float alpha, int accumulate = 0) {
   dim3 grid(ceil_div(N, 64), ceil_div(M, 64), batch);
-  B200_LAUNCH((gemm_nt_kernel<TA, TB, TC>), grid, 256, 0, st, A, lda, sa, B, ldb, sb, C, ldc, sc, M, N, K, alpha);
+  B200_LAUNCH((gemm_nt_kernel<TA, TB, TC>), grid, 256, 0, st, A, lda, sa, B, ldb, sb, C, ldc, sc, M, N, K, alpha, accumulate);
   return check_launch("gemm_nt");
 }
 
@@ -581,29 +586,60 @@ int launch_scan_r(cudaStream_t st, const ScanParams& p, int n_entries) {
   return check_launch("matrix_memory_scan");
 }
 
-// prep rows (q, k and the decay or the two gates, fp32) for every token of the step, then the recurrence per (request, head)
+// prep rows (q, k and the decay or the two gates, fp32) for every token of the step, then the recurrence per (request, head);
+// long portions run as segments side by side, are chained, and their later segments get the carried state's share added
 template <typename T, int MODE>
 int launch_scan(b200_dlm* h, ScanParams p, int n_tok) {
+  cudaStream_t st = h->stream;
   p.prow = ((MODE == MODE_DECAY ? 3 : 2) * p.dim + (MODE == MODE_EXPGATE ? 2 : 0) + 3) / 4 * 4;
   p.prep = h->scan_prep; p.vprep = h->scan_v;
   p.vec = p.vdim % 4 == 0;
   p.stage = h->max_entry_tokens <= 8 ? 8 : 16;
   p.ent_par = h->meta_dev + h->off_ent_par; p.slots = h->slots;
-  B200_LAUNCH((scan_prep_kernel<T, MODE>), n_tok, 256, 0, h->stream, p);
+  p.ent_seg = h->meta_dev + h->off_ent_seg; p.ent_nseg = h->meta_dev + h->off_ent_nseg; p.ent_buf = h->meta_dev + h->off_ent_buf;
+  p.segS = h->segS; p.segB = h->segB; p.segM = h->segM; p.qb = h->gate32; p.tokM = h->tokM;      // the decay logits are spent once prep has run
+  B200_LAUNCH((scan_prep_kernel<T, MODE>), n_tok, 256, 0, st, p);
   B200_TRY(check_launch("scan_prep"));
   // a few long requests: 16 lanes per column (twice the CTAs, half the chain per token); batches and single tokens: 8 lanes per
   // column (state rows read in full sectors).  Measured on 2048-token prompts, 8 heads of 128 x 256: 8 / 16 / 32 lanes per
   // column 0.90 / 0.82 / 0.98 ms per layer; 16 lanes sharing 2 columns per thread 1.22 ms (fewer warps to overlap the chains).
-  const bool wide = h->max_entry_tokens > 8 && h->n_entries * p.heads * ceil_div(p.vdim, 16) < 2 * 148 && p.dim > 16;
+  const int nu = h->n_units;
+  const bool wide = h->max_entry_tokens > 8 && nu * p.heads * ceil_div(p.vdim, 16) < 2 * 148 && p.dim > 16;
+  int rc;
   if (wide) {
-    if (p.dim <= 64) return launch_scan_r<MODE, 4, 16, 1>(h->stream, p, h->n_entries);
-    if (p.dim <= 128) return launch_scan_r<MODE, 8, 16, 1>(h->stream, p, h->n_entries);
-    return launch_scan_r<MODE, 16, 16, 1>(h->stream, p, h->n_entries);
+    if (p.dim <= 64) rc = launch_scan_r<MODE, 4, 16, 1>(st, p, nu);
+    else if (p.dim <= 128) rc = launch_scan_r<MODE, 8, 16, 1>(st, p, nu);
+    else rc = launch_scan_r<MODE, 16, 16, 1>(st, p, nu);
+  } else {
+    if (p.dim <= 32) rc = launch_scan_r<MODE, 4, 8, 1>(st, p, nu);
+    else if (p.dim <= 64) rc = launch_scan_r<MODE, 8, 8, 1>(st, p, nu);
+    else if (p.dim <= 128) rc = launch_scan_r<MODE, 16, 8, 1>(st, p, nu);
+    else rc = launch_scan_r<MODE, 32, 8, 1>(st, p, nu);
   }
-  if (p.dim <= 32) return launch_scan_r<MODE, 4, 8, 1>(h->stream, p, h->n_entries);
-  if (p.dim <= 64) return launch_scan_r<MODE, 8, 8, 1>(h->stream, p, h->n_entries);
-  if (p.dim <= 128) return launch_scan_r<MODE, 16, 8, 1>(h->stream, p, h->n_entries);
-  return launch_scan_r<MODE, 32, 8, 1>(h->stream, p, h->n_entries);
+  B200_TRY(rc);
+  bool any = false;
+  for (auto& u : h->units) any |= u.buf >= 0;
+  if (!any) return B200_OK;
+  B200_LAUNCH(scan_chain_kernel<MODE>, nu * p.heads, 256, 0, st, p);
+  B200_TRY(check_launch("scan_chain"));
+  const long long H = p.heads, D = p.dim, V = p.vdim;
+  for (auto& u : h->units) {
+    if (u.buf < 0 || u.seg == 0) continue;
+    const float* start = h->segS + (long long)u.buf * H * (V + 1) * D;        // the segment's true start state, [heads][vdim + 1][dim]
+    float* out = p.out + (long long)u.tok0 * H * V;
+    if (MODE == MODE_DECAY) {      // out += (q . decay so far) S_start
+      B200_TRY(gemm_nt(st, h->gate32 + (long long)u.tok0 * H * D, H * D, D, start, D, (V + 1) * D, out, H * V, V, u.ntok, (int)V, (int)D, (int)H, 1.f, 1));
+    } else {                       // [S_start^T q | n_start . q], then the weighted meeting with the local numerators
+      float* corr = h->corr + (long long)u.tok0 * H * (V + 1);
+      B200_TRY(gemm_nt(st, h->scan_prep + (long long)u.tok0 * H * p.prow, H * p.prow, (long long)p.prow, start, D, (V + 1) * D, corr, H * (V + 1), V + 1, u.ntok,
+                       (int)V + 1, (int)D, (int)H, 1.f));
+      const long long rows = (long long)u.ntok * H;
+      B200_LAUNCH(mlstm_combine_kernel, (unsigned)ceil_div64(rows, 4), 128, 0, st, out, corr, h->tokM + (long long)u.tok0 * H * 4, h->segM + (long long)u.buf * H * 4,
+                  (int)H, (int)V, rows);
+      B200_TRY(check_launch("mlstm_combine"));
+    }
+  }
+  return B200_OK;
 }
 
 template <typename T>
@@ -873,6 +909,8 @@ int b200_dlm_set_option(b200_dlm* h, const char* name, int value) {
     h->attn_tc = value < 0 ? 0 : value;      // 2: the tensor-core window attention also for single-token requests
   } else if (n == "time_kernels") {
     h->time_kernels = value != 0;
+  } else if (n == "scan_segment") {
+    h->scan_seg = value < 8 ? 8 : value;
   } else if (n == "attn_split") {
     h->attn_split = value < 0 ? 0 : value;
   } else {
@@ -1010,7 +1048,7 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
   const size_t T = (size_t)max_step_tokens, W = (size_t)c.width;
   h->stream = static_cast<cudaStream_t>(stream);
   const bool sandwich = c.block == B200_BLOCK_SANDWICH;
-  size_t max_ldp = 0, max_hr = 0, max_hv = 0, max_ff = 1, max_r = 0, max_tiles = 0, max_qkv = 1, max_rv = 1, max_gate = 1, max_e = 1, max_top = 0, max_part = 0, max_prep = 4;
+  size_t max_ldp = 0, max_hr = 0, max_hv = 0, max_ff = 1, max_r = 0, max_tiles = 0, max_qkv = 1, max_rv = 1, max_gate = 1, max_e = 1, max_top = 0, max_part = 0, max_prep = 4, max_segrow = 1, max_heads = 1;
   for (auto& L : h->layers) {
     const b200_dlm_mixer &a = L.c.a, &b = L.c.b;
     max_ldp = std::max(max_ldp, (size_t)L.ldp);
@@ -1034,6 +1072,8 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
       max_rv = std::max(max_rv, (size_t)b.heads * b.vdim);
       max_gate = std::max(max_gate, (size_t)b.heads * b.dim);
       max_prep = std::max(max_prep, (size_t)b.heads * (3 * b.dim + 4));
+      max_segrow = std::max(max_segrow, (size_t)b.heads * (b.vdim + 1) * b.dim);
+      max_heads = std::max(max_heads, (size_t)b.heads);
       max_part = std::max(max_part, (size_t)(L.sig_mma >= 0 ? 16 : L.QT) * a.heads * (a.vdim + 2));
     } else {
       B200_TRY(A.alloc_t(&L.St, (size_t)slots * a.heads * a.vdim * a.dim));
@@ -1042,6 +1082,9 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
       max_rv = std::max(max_rv, (size_t)a.heads * a.vdim);
       max_gate = std::max(max_gate, (size_t)2 * a.heads);
       max_prep = std::max(max_prep, (size_t)a.heads * (2 * a.dim + 8));
+      max_segrow = std::max(max_segrow, (size_t)a.heads * (a.vdim + 1) * a.dim);
+      max_heads = std::max(max_heads, (size_t)a.heads);
+      max_gate = std::max(max_gate, (size_t)a.heads * a.dim);
     }
     if (L.c.mlp == B200_MLP_MOE_RELU2) { max_e = std::max(max_e, (size_t)L.c.experts); max_top = std::max(max_top, (size_t)L.c.top); }
   }
@@ -1058,6 +1101,13 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
     B200_TRY(A.alloc_t(&h->scan32, T * max_rv));
     B200_TRY(A.alloc_t(&h->scan_v, T * max_rv));
     B200_TRY(A.alloc_t(&h->scan_prep, T * max_prep));
+    h->max_seg_units = max_step_tokens / 8 + 2;       // segments are at least 8 tokens
+    B200_TRY(A.alloc_t(&h->segS, (size_t)(max_step_tokens / std::max(h->scan_seg, 8) + 2) * max_segrow));
+    B200_TRY(A.alloc_t(&h->segB, (size_t)(max_step_tokens / std::max(h->scan_seg, 8) + 2) * max_gate));
+    B200_TRY(A.alloc_t(&h->segM, (size_t)(max_step_tokens / std::max(h->scan_seg, 8) + 2) * max_heads * 4));
+    B200_TRY(A.alloc_t(&h->tokM, T * max_heads * 4));
+    B200_TRY(A.alloc_t(&h->corr, T * (max_rv + max_heads)));
+    h->max_seg_units = max_step_tokens / std::max(h->scan_seg, 8) + 2;
     B200_TRY(A.alloc_t(&h->gate32, T * max_gate));
     B200_TRY(A.alloc_t(&h->attn32, T * max_hv));
     B200_TRY(A.alloc(&h->obuf2, T * max_rv * es));
@@ -1101,7 +1151,10 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
   h->off_want = off; off += max_want;
   h->off_first = off; off += max_step_tokens;
   h->off_last = off; off += max_step_tokens;
-  const int max_entries = std::min(slots, max_step_tokens);
+  const int max_entries = std::min(slots, max_step_tokens) + max_step_tokens / 8 + 2;      // entries, and the segments long portions are cut into
+  h->off_ent_seg = off; off += max_entries;
+  h->off_ent_nseg = off; off += max_entries;
+  h->off_ent_buf = off; off += max_entries;
   h->off_ent_tok0 = off; off += max_entries;
   h->off_ent_ntok = off; off += max_entries;
   h->off_ent_slot = off; off += max_entries;
@@ -1160,7 +1213,8 @@ int b200_dlm_step(b200_dlm* h, int n_entries, const int32_t* slots_host, const i
   // the previous step's metadata copy must have left the pinned block
   B200_CUDA(cudaEventSynchronize(h->ev_meta));
   int* m = h->meta_pin;
-  int t = 0, max_ctx = 0;
+  int t = 0, max_ctx = 0, n_seg_units = 0;
+  h->units.clear();
   for (auto& s : h->sigs) s.count = 0;
   for (int e = 0; e < n_entries; ++e) {
     const int s = slots_host[e], n = counts_host[e], base = h->len[s];
@@ -1173,8 +1227,18 @@ int b200_dlm_step(b200_dlm* h, int n_entries, const int32_t* slots_host, const i
         ++sg.count;
       }
     }
-    m[h->off_ent_tok0 + e] = t; m[h->off_ent_ntok + e] = n; m[h->off_ent_slot + e] = s; m[h->off_ent_pos0 + e] = base;
-    m[h->off_ent_par + e] = h->par[s];
+    {   // the recurrences' units: the entry itself, or its segments when it is long
+      const int seg_len = h->scan_seg, nseg = (h->cfg.block == B200_BLOCK_SANDWICH && n >= 2 * seg_len && n_seg_units + ceil_div(n, seg_len) <= h->max_seg_units) ? ceil_div(n, seg_len) : 1;
+      for (int q = 0; q < nseg; ++q) {
+        const int u = (int)h->units.size();
+        const int u_tok0 = t + q * seg_len, u_n = nseg == 1 ? n : std::min(seg_len, n - q * seg_len);
+        m[h->off_ent_tok0 + u] = u_tok0; m[h->off_ent_ntok + u] = u_n; m[h->off_ent_slot + u] = s; m[h->off_ent_pos0 + u] = base;
+        m[h->off_ent_par + u] = h->par[s];
+        m[h->off_ent_seg + u] = q; m[h->off_ent_nseg + u] = nseg; m[h->off_ent_buf + u] = nseg > 1 ? n_seg_units : 0;
+        h->units.push_back({u_tok0, u_n, q, nseg > 1 ? n_seg_units : -1});
+        if (nseg > 1) ++n_seg_units;
+      }
+    }
     const int first = t, lastt = t + n - 1;
     for (int i = 0; i < n; ++i, ++t) {
       m[h->off_tok + t] = tokens_host[t];
@@ -1189,6 +1253,7 @@ int b200_dlm_step(b200_dlm* h, int n_entries, const int32_t* slots_host, const i
   B200_CUDA(cudaMemcpyAsync(h->meta_dev, m, (size_t)h->meta_ints * sizeof(int), cudaMemcpyHostToDevice, h->stream));
   B200_CUDA(cudaEventRecord(h->ev_meta, h->stream));
   h->n_entries = n_entries;
+  h->n_units = (int)h->units.size();
   h->max_entry_tokens = 0;
   for (int e = 0; e < n_entries; ++e) h->max_entry_tokens = std::max(h->max_entry_tokens, (int)counts_host[e]);
   int rc;

@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(256) relu2_kernel(const T* __restrict__ proj, 
 template <typename TA, typename TB, typename TC>
 __global__ void __launch_bounds__(256) gemm_nt_kernel(const TA* __restrict__ A, long long lda, long long sa, const TB* __restrict__ B,
                                                       long long ldb, long long sb, TC* __restrict__ C, long long ldc, long long sc,
-                                                      int M, int N, int K, float alpha) {
+                                                      int M, int N, int K, float alpha, int accumulate = 0) {
   constexpr int BM = 64, BN = 64, BK = 16;
   __shared__ float As[BK][BM + 1], Bs[BK][BN + 1];
   A += (long long)blockIdx.z * sa; B += (long long)blockIdx.z * sb; C += (long long)blockIdx.z * sc;
@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(256) gemm_nt_kernel(const TA* __restrict__ A, 
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int m = m0 + ty + 16 * i, n = n0 + tx + 16 * j;
-      if (m < M && n < N) C[(long long)m * ldc + n] = from_f<TC>(alpha * acc[i][j]);
+      if (m < M && n < N) C[(long long)m * ldc + n] = from_f<TC>(alpha * acc[i][j] + (accumulate ? to_f(C[(long long)m * ldc + n]) : 0.f));
     }
 }
 

@@ -568,6 +568,16 @@ struct ScanParams {
   float* mval;              // MODE_EXPGATE: [2][slots][heads]                has already replaced
   const int* ent_par;       // per entry: the generation to read (the other one is written)
   int slots;
+  // Long portions are cut into segments that run as entries of their own, in parallel (ent_seg = index of the segment in its
+  // portion, ent_nseg = segments of the portion, ent_buf = its row of the segment buffers).  Segment 0 continues the slot's
+  // state; the others start from nothing and leave what scan_chain_kernel and the correction need:
+  //   segS  [buf][heads][vdim + 1][dim]  the segment's end state (row vdim: mLSTM's n), later replaced by its true start state
+  //   segB  [buf][heads][dim]            MODE_DECAY: product of the decays over the segment
+  //   segM  [buf][heads][4]              MODE_EXPGATE: sum of the log forget gates, local maximum at the end, (chain: true maximum at the start)
+  //   qb    [tokens][heads * dim]        MODE_DECAY: q times the product of the decays from the segment's start to the token
+  //   tokM  [tokens][heads][4]           MODE_EXPGATE: log forget sum so far, local maximum, local n . q
+  const int* ent_seg; const int* ent_nseg; const int* ent_buf;
+  float *segS, *segB, *segM, *qb, *tokM;
   const int* ent_tok0;      // per entry: first token of the step, number of tokens, slot, position of the first token
   const int* ent_ntok;
   const int* ent_slot;
@@ -630,6 +640,9 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
   const int rg = threadIdx.x & (LPC - 1), cl = threadIdx.x / LPC * CB, col = blockIdx.y * NC + cl;      // first of the thread's columns
   float* Sbase = p.St + ((long long)slot * heads + head) * vdim * dim;
   const int par = MODE == MODE_EXPGATE ? p.ent_par[ent] : 0;
+  const int seg = p.ent_seg[ent], nseg = p.ent_nseg[ent];
+  const long long sbuf = (long long)p.ent_buf[ent] * heads + head;      // row of the segment buffers (when nseg > 1)
+  const bool lead = blockIdx.y == 0 && cl == 0;                          // the threads that write what exists once per head
   const long long sh = (long long)slot * heads + head;
   const float* nin = MODE == MODE_EXPGATE ? p.nvec + ((long long)par * p.slots * heads + sh) * dim : nullptr;
   float* nout = MODE == MODE_EXPGATE ? p.nvec + ((long long)(par ^ 1) * p.slots * heads + sh) * dim : nullptr;
@@ -637,12 +650,16 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
 #pragma unroll
   for (int i = 0; i < R; ++i) {
     const int r = rg + LPC * i;
-    const bool live = pos0 > 0 && r < dim;
+    const bool live = pos0 > 0 && seg == 0 && r < dim;
 #pragma unroll
     for (int j = 0; j < CB; ++j) S[i][j] = live && col + j < vdim ? Sbase[(long long)(col + j) * dim + r] : 0.f;
     nv[i] = (MODE == MODE_EXPGATE && live) ? nin[r] : 0.f;
   }
-  if (MODE == MODE_EXPGATE && pos0 > 0) m = p.mval[(long long)par * p.slots * heads + sh];
+  if (MODE == MODE_EXPGATE && pos0 > 0 && seg == 0) m = p.mval[(long long)par * p.slots * heads + sh];
+  if (MODE == MODE_EXPGATE && seg > 0) m = -INFINITY;        // a later segment: nothing seen yet (the first token sets the maximum)
+  float bdec[MODE == MODE_DECAY ? R : 1], logF = 0.f;         // later segments: decay products per row; sum of the log forget gates
+#pragma unroll
+  for (int i = 0; i < (MODE == MODE_DECAY ? R : 1); ++i) bdec[i] = 1.f;
 
   auto issue = [&](int t0, int buf) {
     const int tn = min(TT, nt - t0);
@@ -684,9 +701,10 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
       if (MODE == MODE_EXPGATE) {
         const float il = aa[0], fl = aa[1];
         m2 = fmaxf(fl + m, il);
-        fa = expf(fl + m - m2);
+        fa = expf(fl + m - m2);                      // m = -inf (nothing seen yet) gives 0
         fb = expf(il - m2);
         m = m2;
+        logF += fl;
       }
 #pragma unroll
       for (int i = 0; i < R; ++i) {
@@ -694,6 +712,10 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
         if (r < dim) {
           const float kv = kk[r] * fb, qv = qq[r];
           const float ar = MODE == MODE_DECAY ? aa[r] : fa;
+          if (MODE == MODE_DECAY && seg > 0) {
+            bdec[i] *= ar;
+            if (lead) p.qb[(long long)(tok0 + t0 + tt) * heads * dim + head * dim + r] = qv * bdec[i];
+          }
 #pragma unroll
           for (int j = 0; j < CB; ++j) {
             S[i][j] = fmaf(ar, S[i][j], kv * v[j]);
@@ -712,9 +734,14 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
       if (MODE == MODE_EXPGATE) {
 #pragma unroll
         for (int o = 1; o < LPC; o <<= 1) nq += __shfl_xor_sync(0xffffffffu, nq, o);
-        const float den = 1.f / (fmaxf(fabsf(nq), expf(-m2)) + 1e-6f);
+        if (seg == 0) {
+          const float den = 1.f / (fmaxf(fabsf(nq), expf(-m2)) + 1e-6f);
 #pragma unroll
-        for (int j = 0; j < CB; ++j) acc[j] *= den;
+          for (int j = 0; j < CB; ++j) acc[j] *= den;
+        } else if (lead && rg == 0) {      // numerators stay as they are; the correction divides
+          float* tm = p.tokM + ((long long)(tok0 + t0 + tt) * heads + head) * 4;
+          tm[0] = logF; tm[1] = m2; tm[2] = nq;
+        }
       }
       if (rg == 0) {
         float* o = p.out + (long long)(tok0 + t0 + tt) * heads * vdim + head * vdim + col;
@@ -724,16 +751,90 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
     }
     __syncthreads();
   }
+  if (nseg > 1) {      // a segment of a long portion: its end state goes to the segment buffers, scan_chain_kernel finishes the slot
+    float* dst = p.segS + sbuf * (vdim + 1) * dim;
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int r = rg + LPC * i;
+      if (r < dim) {
+#pragma unroll
+        for (int j = 0; j < CB; ++j) if (col + j < vdim) dst[(long long)(col + j) * dim + r] = S[i][j];
+        if (MODE == MODE_EXPGATE && lead) dst[(long long)vdim * dim + r] = nv[i];
+        if (MODE == MODE_DECAY && lead) p.segB[sbuf * dim + r] = bdec[i];
+      }
+    }
+    if (MODE == MODE_EXPGATE && lead && rg == 0) { p.segM[sbuf * 4] = logF; p.segM[sbuf * 4 + 1] = m; }
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < R; ++i) {
     const int r = rg + LPC * i;
     if (r < dim) {
 #pragma unroll
       for (int j = 0; j < CB; ++j) if (col + j < vdim) Sbase[(long long)(col + j) * dim + r] = S[i][j];
-      if (MODE == MODE_EXPGATE && blockIdx.y == 0 && cl == 0) nout[r] = nv[i];
+      if (MODE == MODE_EXPGATE && lead) nout[r] = nv[i];
     }
   }
-  if (MODE == MODE_EXPGATE && blockIdx.y == 0 && threadIdx.x == 0) p.mval[(long long)(par ^ 1) * p.slots * heads + sh] = m;
+  if (MODE == MODE_EXPGATE && lead && rg == 0) p.mval[(long long)(par ^ 1) * p.slots * heads + sh] = m;
+}
+
+// After the segments of a long portion have run side by side: walks them in order, per (portion, head) and state element,
+//   MODE_DECAY:   start_p = S;  S <- B_p * S + end_p                                   (B_p: the segment's decay product, per row)
+//   MODE_EXPGATE: start_p = S;  m' = max(F_p + m, ml_p);  S <- e^(F_p + m - m') S + e^(ml_p - m') end_p   (n likewise; F_p: log forget sum)
+// leaving every later segment's true start state in its row of segS (and its starting maximum in segM[2]) for the correction, and
+// the state after the last segment in the slot.  Grid: entries * heads; the CTA of a segment other than a first one returns.
+template <int MODE>
+__global__ void __launch_bounds__(256) scan_chain_kernel(ScanParams p) {
+  const int ent = blockIdx.x / p.heads, head = blockIdx.x - ent * p.heads;
+  const int nseg = p.ent_nseg[ent];
+  if (p.ent_seg[ent] != 0 || nseg < 2) return;
+  const int heads = p.heads, dim = p.dim, vdim = p.vdim, slot = p.ent_slot[ent], buf0 = p.ent_buf[ent];
+  const long long sh = (long long)slot * heads + head;
+  const int par = MODE == MODE_EXPGATE ? p.ent_par[ent] : 0;
+  const int rows = MODE == MODE_EXPGATE ? vdim + 1 : vdim;
+  const long long bstride = (long long)heads * (vdim + 1) * dim;
+  float* s0 = p.segS + ((long long)buf0 * heads + head) * (vdim + 1) * dim;
+  for (int e = threadIdx.x; e < rows * dim; e += 256) {
+    const int r = e % dim;
+    float S = s0[e];
+    float m = MODE == MODE_EXPGATE ? p.segM[((long long)buf0 * heads + head) * 4 + 1] : 0.f;
+    for (int q = 1; q < nseg; ++q) {
+      const long long sb = (long long)(buf0 + q) * heads + head;
+      const float end = s0[q * bstride + e];
+      s0[q * bstride + e] = S;
+      if (MODE == MODE_DECAY) {
+        S = fmaf(p.segB[sb * dim + r], S, end);
+      } else {
+        const float F = p.segM[sb * 4], ml = p.segM[sb * 4 + 1];
+        const float m2 = fmaxf(F + m, ml);
+        S = expf(F + m - m2) * S + expf(ml - m2) * end;
+        if (e == 0) p.segM[sb * 4 + 2] = m;        // the maximum this segment truly starts from
+        m = m2;
+      }
+    }
+    if (e < vdim * dim) p.St[sh * vdim * dim + e] = S;
+    else p.nvec[((long long)(par ^ 1) * p.slots * heads + sh) * dim + r] = S;
+    if (MODE == MODE_EXPGATE && e == 0) p.mval[(long long)(par ^ 1) * p.slots * heads + sh] = m;
+  }
+}
+
+// mLSTM, tokens of a later segment: the carried part corr = [S_start^T q | n_start . q] (one small product per segment) meets the
+// local numerators:  m = max(F_t + m_start, ml_t);  a = e^(F_t + m_start - m), b = e^(ml_t - m);
+//   out = (a corr + b local) / (max(|a corr_n + b local_n|, e^(-m)) + 1e-6).  One warp per (token, head).
+__global__ void __launch_bounds__(128) mlstm_combine_kernel(float* __restrict__ out, const float* __restrict__ corr, const float* __restrict__ tokM,
+                                                            const float* __restrict__ segM_row, int heads, int vdim, long long rows) {
+  const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int h = (int)(row % heads);
+  const float* tm = tokM + row * 4;
+  const float ms = segM_row[h * 4 + 2];
+  const float m = fmaxf(tm[0] + ms, tm[1]);
+  const float a = expf(tm[0] + ms - m), b = expf(tm[1] - m);
+  const float* c = corr + row * (vdim + 1);
+  const float den = 1.f / (fmaxf(fabsf(a * c[vdim] + b * tm[2]), expf(-m)) + 1e-6f);
+  float* o = out + row * vdim;
+  for (int i = lane; i < vdim; i += 32) o[i] = (a * c[i] + b * o[i]) * den;
 }
 
 // what leaves a recurrent mixer: per head rms_norm over vdim (weight w[h * wstride + c]: wstride = 0 shares one row between

@@ -378,3 +378,40 @@ def test_window_attention_on_tensor_cores(heads, kv, dim, vdim, size):
         parts += [gen.step([(2, [t])], [0]) for t in toks[125:]]
         assert_close(torch.cat(parts), want, torch.bfloat16, "portions and single tokens")
         assert gen.error_flags() == 0
+
+
+@pytest.mark.parametrize("cfg", [ODD, ALIGNED], ids=["odd", "aligned"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_long_portions_run_as_parallel_segments(dtype, cfg):
+    """A portion of at least two segments is cut for the recurrences: the segments run side by side from empty memories, are
+    chained, and the later ones get the carried state's share added.  Segments of 16 tokens here (256 by default), so that
+    portions of 33 .. 150 tokens take that path: one prompt, portions with a ragged last segment, a batch of long and short
+    requests on different histories, then single tokens on the state the chain left in the slot."""
+    from moshi_b200 import _lib
+    model, orc = build(cfg, dtype)
+    _lib.check(model._lib.b200_dlm_set_option(model._h, b"scan_segment", 16))
+    reqs = [tokens(150, cfg.vocab, 80), tokens(9, cfg.vocab, 81), tokens(120, cfg.vocab, 82)]
+    want = [orc.forward(r) for r in reqs]
+    with gen_for(model) as gen:
+        assert_close(gen.step([(0, reqs[0])], list(range(150))), want[0], dtype, "one portion of 150 tokens")
+        gen.release(0)
+        parts = [gen.step([(0, reqs[0][:70])], list(range(70))), gen.step([(0, reqs[0][70:73])], [0, 1, 2]), gen.step([(0, reqs[0][73:110])], list(range(37)))]
+        parts += [gen.step([(0, [t])], [0]) for t in reqs[0][110:]]
+        assert_close(torch.cat(parts), want[0], dtype, "70 + 3 + 37 tokens, then one by one")
+        gen.release(0)
+        gen.step([(2, reqs[0][:40]), (0, reqs[2][:33])])
+        got = gen.step([(2, reqs[0][40:]), (1, reqs[1]), (0, reqs[2][33:])], list(range(110 + 9 + 87)))
+        assert_close(got[:110], want[0][40:], dtype, "110 tokens on a history of 40")
+        assert_close(got[110:119], want[1], dtype, "a short fresh request beside them")
+        assert_close(got[119:], want[2][33:], dtype, "87 tokens on a history of 33")
+        assert gen.error_flags() == 0
+
+
+def test_segments_of_the_default_length():
+    cfg = ALIGNED
+    model, orc = build(cfg, torch.float32, seed=13)
+    toks = tokens(700, cfg.vocab, 90)
+    want = orc.forward(toks)
+    with gen_for(model, capacity=1024, max_step_tokens=1024) as gen:
+        got = torch.cat([gen.step([(0, toks[:600])], list(range(600))), gen.step([(0, toks[600:])], list(range(100)))])
+    assert_close(got, want, torch.float32)
