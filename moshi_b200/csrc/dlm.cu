@@ -166,9 +166,10 @@ int seal_weight(b200_dlm* h, Weight& w, void* rm, int N, int K, std::vector<void
 
 template <typename TA, typename TB, typename TC>
 int gemm_nt(cudaStream_t st, const TA* A, long long lda, long long sa, const TB* B, long long ldb, long long sb, TC* C, long long ldc,
-            long long sc, int M, int N, int K, int batch, float alpha, int accumulate = 0) {
-  dim3 grid(ceil_div(N, 64), ceil_div(M, 64), batch);
-  B200_LAUNCH((gemm_nt_kernel<TA, TB, TC>), grid, 256, 0, st, A, lda, sa, B, ldb, sb, C, ldc, sc, M, N, K, alpha, accumulate);
+            long long sc, int M, int N, int K, int batch, float alpha, int accumulate = 0, int outer = 1, long long sa2 = 0, long long sb2 = 0,
+            long long sc2 = 0) {
+  dim3 grid(ceil_div(N, 64), ceil_div(M, 64), batch * outer);
+  B200_LAUNCH((gemm_nt_kernel<TA, TB, TC>), grid, 256, 0, st, A, lda, sa, B, ldb, sb, C, ldc, sc, M, N, K, alpha, accumulate, outer > 1 ? batch : 0, sa2, sb2, sc2);
   return check_launch("gemm_nt");
 }
 
@@ -594,7 +595,7 @@ int launch_scan(b200_dlm* h, ScanParams p, int n_tok) {
   p.prow = ((MODE == MODE_DECAY ? 3 : 2) * p.dim + (MODE == MODE_EXPGATE ? 2 : 0) + 3) / 4 * 4;
   p.prep = h->scan_prep; p.vprep = h->scan_v;
   p.vec = p.vdim % 4 == 0;
-  p.stage = h->max_entry_tokens <= 8 ? 8 : 16;
+  p.stage = 8;      // short stages: less shared memory per CTA, more CTAs per SM to overlap the chains
   p.ent_par = h->meta_dev + h->off_ent_par; p.slots = h->slots;
   p.ent_seg = h->meta_dev + h->off_ent_seg; p.ent_nseg = h->meta_dev + h->off_ent_nseg; p.ent_buf = h->meta_dev + h->off_ent_buf;
   p.segS = h->segS; p.segB = h->segB; p.segM = h->segM; p.qb = h->gate32; p.tokM = h->tokM;      // the decay logits are spent once prep has run
@@ -620,24 +621,34 @@ int launch_scan(b200_dlm* h, ScanParams p, int n_tok) {
   bool any = false;
   for (auto& u : h->units) any |= u.buf >= 0;
   if (!any) return B200_OK;
-  B200_LAUNCH(scan_chain_kernel<MODE>, nu * p.heads, 256, 0, st, p);
+  B200_LAUNCH(scan_chain_kernel<MODE>, dim3(nu * p.heads, ceil_div((p.vdim + 1) * p.dim, 256)), 256, 0, st, p);
   B200_TRY(check_launch("scan_chain"));
+  // the carried state's share for the later segments: runs of segments of one portion with equal length go as one batched product
   const long long H = p.heads, D = p.dim, V = p.vdim;
-  for (auto& u : h->units) {
-    if (u.buf < 0 || u.seg == 0) continue;
-    const float* start = h->segS + (long long)u.buf * H * (V + 1) * D;        // the segment's true start state, [heads][vdim + 1][dim]
+  for (size_t i = 0; i < h->units.size();) {
+    const auto& u = h->units[i];
+    if (u.buf < 0 || u.seg == 0) { ++i; continue; }
+    size_t j = i + 1;
+    while (j < h->units.size() && h->units[j].buf == h->units[j - 1].buf + 1 && h->units[j].seg == h->units[j - 1].seg + 1 && h->units[j].ntok == u.ntok) ++j;
+    const int run = (int)(j - i);
+    const float* start = h->segS + (long long)u.buf * H * (V + 1) * D;        // the segments' true start states, [run][heads][vdim + 1][dim]
     float* out = p.out + (long long)u.tok0 * H * V;
     if (MODE == MODE_DECAY) {      // out += (q . decay so far) S_start
-      B200_TRY(gemm_nt(st, h->gate32 + (long long)u.tok0 * H * D, H * D, D, start, D, (V + 1) * D, out, H * V, V, u.ntok, (int)V, (int)D, (int)H, 1.f, 1));
+      B200_TRY(gemm_nt(st, h->gate32 + (long long)u.tok0 * H * D, H * D, D, start, D, (V + 1) * D, out, H * V, V, u.ntok, (int)V, (int)D, (int)H, 1.f, 1,
+                       run, (long long)u.ntok * H * D, H * (V + 1) * D, (long long)u.ntok * H * V));
     } else {                       // [S_start^T q | n_start . q], then the weighted meeting with the local numerators
       float* corr = h->corr + (long long)u.tok0 * H * (V + 1);
       B200_TRY(gemm_nt(st, h->scan_prep + (long long)u.tok0 * H * p.prow, H * p.prow, (long long)p.prow, start, D, (V + 1) * D, corr, H * (V + 1), V + 1, u.ntok,
-                       (int)V + 1, (int)D, (int)H, 1.f));
-      const long long rows = (long long)u.ntok * H;
-      B200_LAUNCH(mlstm_combine_kernel, (unsigned)ceil_div64(rows, 4), 128, 0, st, out, corr, h->tokM + (long long)u.tok0 * H * 4, h->segM + (long long)u.buf * H * 4,
-                  (int)H, (int)V, rows);
+                       (int)V + 1, (int)D, (int)H, 1.f, 0, run, (long long)u.ntok * H * p.prow, H * (V + 1) * D, (long long)u.ntok * H * (V + 1)));
+      for (size_t k = i; k < j; ++k) {
+        const auto& w = h->units[k];
+        const long long rows = (long long)w.ntok * H;
+        B200_LAUNCH(mlstm_combine_kernel, (unsigned)ceil_div64(rows, 4), 128, 0, st, p.out + (long long)w.tok0 * H * V, h->corr + (long long)w.tok0 * H * (V + 1),
+                    h->tokM + (long long)w.tok0 * H * 4, h->segM + (long long)w.buf * H * 4, (int)H, (int)V, rows);
+      }
       B200_TRY(check_launch("mlstm_combine"));
     }
+    i = j;
   }
   return B200_OK;
 }
@@ -1101,7 +1112,6 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
     B200_TRY(A.alloc_t(&h->scan32, T * max_rv));
     B200_TRY(A.alloc_t(&h->scan_v, T * max_rv));
     B200_TRY(A.alloc_t(&h->scan_prep, T * max_prep));
-    h->max_seg_units = max_step_tokens / 8 + 2;       // segments are at least 8 tokens
     B200_TRY(A.alloc_t(&h->segS, (size_t)(max_step_tokens / std::max(h->scan_seg, 8) + 2) * max_segrow));
     B200_TRY(A.alloc_t(&h->segB, (size_t)(max_step_tokens / std::max(h->scan_seg, 8) + 2) * max_gate));
     B200_TRY(A.alloc_t(&h->segM, (size_t)(max_step_tokens / std::max(h->scan_seg, 8) + 2) * max_heads * 4));

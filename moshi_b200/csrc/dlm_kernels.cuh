@@ -133,13 +133,18 @@ __global__ void __launch_bounds__(256) relu2_kernel(const T* __restrict__ proj, 
 // C[z][M][N] = alpha * A[z][M][K] . B[z][N][K]^T on the CUDA cores (fp32 FMA; inputs converted on load): the all-fp32 mode's
 // linear, the per-head products around the latent attention, and the bf16 mode's linear for shapes the tcgen05 GEMM does not take.
 // A row's sum runs over k in order whatever M is: a token's result does not depend on what else is in the step.
+// accumulate: C += instead of C =.
 template <typename TA, typename TB, typename TC>
 __global__ void __launch_bounds__(256) gemm_nt_kernel(const TA* __restrict__ A, long long lda, long long sa, const TB* __restrict__ B,
                                                       long long ldb, long long sb, TC* __restrict__ C, long long ldc, long long sc,
-                                                      int M, int N, int K, float alpha, int accumulate = 0) {
+                                                      int M, int N, int K, float alpha, int accumulate = 0, int zdiv = 0,
+                                                      long long sa2 = 0, long long sb2 = 0, long long sc2 = 0) {
   constexpr int BM = 64, BN = 64, BK = 16;
   __shared__ float As[BK][BM + 1], Bs[BK][BN + 1];
-  A += (long long)blockIdx.z * sa; B += (long long)blockIdx.z * sb; C += (long long)blockIdx.z * sc;
+  {   // batch index z, or (z / zdiv, z % zdiv) with strides of their own for the outer index (zdiv > 0)
+    const long long z1 = zdiv > 0 ? blockIdx.z % zdiv : blockIdx.z, z2 = zdiv > 0 ? blockIdx.z / zdiv : 0;
+    A += z1 * sa + z2 * sa2; B += z1 * sb + z2 * sb2; C += z1 * sc + z2 * sc2;
+  }
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   float acc[4][4] = {};

@@ -782,7 +782,8 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
 //   MODE_DECAY:   start_p = S;  S <- B_p * S + end_p                                   (B_p: the segment's decay product, per row)
 //   MODE_EXPGATE: start_p = S;  m' = max(F_p + m, ml_p);  S <- e^(F_p + m - m') S + e^(ml_p - m') end_p   (n likewise; F_p: log forget sum)
 // leaving every later segment's true start state in its row of segS (and its starting maximum in segM[2]) for the correction, and
-// the state after the last segment in the slot.  Grid: entries * heads; the CTA of a segment other than a first one returns.
+// the state after the last segment in the slot.  Grid: (entries * heads, state elements / 256); the CTAs of a segment other
+// than a first one return.
 template <int MODE>
 __global__ void __launch_bounds__(256) scan_chain_kernel(ScanParams p) {
   const int ent = blockIdx.x / p.heads, head = blockIdx.x - ent * p.heads;
@@ -794,7 +795,8 @@ __global__ void __launch_bounds__(256) scan_chain_kernel(ScanParams p) {
   const int rows = MODE == MODE_EXPGATE ? vdim + 1 : vdim;
   const long long bstride = (long long)heads * (vdim + 1) * dim;
   float* s0 = p.segS + ((long long)buf0 * heads + head) * (vdim + 1) * dim;
-  for (int e = threadIdx.x; e < rows * dim; e += 256) {
+  const int e = blockIdx.y * 256 + threadIdx.x;      // one state element per thread: the walk over the segments is a chain of loads
+  if (e < rows * dim) {
     const int r = e % dim;
     float S = s0[e];
     float m = MODE == MODE_EXPGATE ? p.segM[((long long)buf0 * heads + head) * 4 + 1] : 0.f;
