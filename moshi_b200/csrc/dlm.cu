@@ -573,17 +573,17 @@ int small_proj(b200_dlm* h, const T* x, long long ldx, const void* w, const floa
   return check_launch("small_proj_f32");
 }
 
-template <int MODE, int R, int LPC, int CB>
+template <int MODE, int R, int LPC, int CB, bool VL = false>
 int launch_scan_r(cudaStream_t st, const ScanParams& p, int n_entries) {
   constexpr int NC = 128 / LPC * CB;
   const dim3 grid(n_entries * p.heads, ceil_div(p.vdim, NC));
   const size_t smem = (size_t)2 * p.stage * (p.prow + NC) * 4;
   static bool attr_set = false;
   if (!attr_set) {
-    B200_CUDA(cudaFuncSetAttribute((matrix_memory_scan_kernel<MODE, R, LPC, CB>), cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+    B200_CUDA(cudaFuncSetAttribute((matrix_memory_scan_kernel<MODE, R, LPC, CB, VL>), cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
     attr_set = true;
   }
-  B200_LAUNCH((matrix_memory_scan_kernel<MODE, R, LPC, CB>), grid, 128, smem, st, p);
+  B200_LAUNCH((matrix_memory_scan_kernel<MODE, R, LPC, CB, VL>), grid, 128, smem, st, p);
   return check_launch("matrix_memory_scan");
 }
 
@@ -592,29 +592,40 @@ int launch_scan_r(cudaStream_t st, const ScanParams& p, int n_entries) {
 template <typename T, int MODE>
 int launch_scan(b200_dlm* h, ScanParams p, int n_tok) {
   cudaStream_t st = h->stream;
-  p.prow = ((MODE == MODE_DECAY ? 3 : 2) * p.dim + (MODE == MODE_EXPGATE ? 2 : 0) + 3) / 4 * 4;
   p.prep = h->scan_prep; p.vprep = h->scan_v;
   p.vec = p.vdim % 4 == 0;
   p.stage = 8;      // short stages: less shared memory per CTA, more CTAs per SM to overlap the chains
   p.ent_par = h->meta_dev + h->off_ent_par; p.slots = h->slots;
   p.ent_seg = h->meta_dev + h->off_ent_seg; p.ent_nseg = h->meta_dev + h->off_ent_nseg; p.ent_buf = h->meta_dev + h->off_ent_buf;
   p.segS = h->segS; p.segB = h->segB; p.segM = h->segM; p.qb = h->gate32; p.tokM = h->tokM;      // the decay logits are spent once prep has run
-  B200_LAUNCH((scan_prep_kernel<T, MODE>), n_tok, 256, 0, st, p);
-  B200_TRY(check_launch("scan_prep"));
   // a few long requests: 16 lanes per column (twice the CTAs, half the chain per token); batches and single tokens: 8 lanes per
-  // column (state rows read in full sectors).  Measured on 2048-token prompts, 8 heads of 128 x 256: 8 / 16 / 32 lanes per
-  // column 0.90 / 0.82 / 0.98 ms per layer; 16 lanes sharing 2 columns per thread 1.22 ms (fewer warps to overlap the chains).
+  // column (state rows read in full sectors).  Portions of more than 8 tokens: the variant whose threads own adjacent rows and
+  // read q, k and the decay four rows per load from lane-ordered prep rows (a third of the instructions per token; its state
+  // accesses are scattered, which costs nothing once per portion but would cost single-token steps twice their time).
   const int nu = h->n_units;
   const bool wide = h->max_entry_tokens > 8 && nu * p.heads * ceil_div(p.vdim, 16) < 2 * 148 && p.dim > 16;
+  const bool lanes4 = h->max_entry_tokens > 8;
+  const int lpc = wide ? 16 : 8;
+  const int rows = wide ? (p.dim <= 64 ? 4 : p.dim <= 128 ? 8 : 16) : (p.dim <= 32 ? 4 : p.dim <= 64 ? 8 : p.dim <= 128 ? 16 : 32);
+  p.lpc = lanes4 ? lpc : 0; p.rows = rows;
+  const int Dp = lanes4 ? lpc * rows : p.dim;
+  p.prow = ((MODE == MODE_DECAY ? 3 : 2) * Dp + (MODE == MODE_EXPGATE ? 2 : 0) + 3) / 4 * 4;
+  B200_LAUNCH((scan_prep_kernel<T, MODE>), n_tok, 256, 0, st, p);
+  B200_TRY(check_launch("scan_prep"));
   int rc;
   if (wide) {
-    if (p.dim <= 64) rc = launch_scan_r<MODE, 4, 16, 1>(st, p, nu);
-    else if (p.dim <= 128) rc = launch_scan_r<MODE, 8, 16, 1>(st, p, nu);
-    else rc = launch_scan_r<MODE, 16, 16, 1>(st, p, nu);
+    if (rows == 4) rc = launch_scan_r<MODE, 4, 16, 1, true>(st, p, nu);
+    else if (rows == 8) rc = launch_scan_r<MODE, 8, 16, 1, true>(st, p, nu);
+    else rc = launch_scan_r<MODE, 16, 16, 1, true>(st, p, nu);
+  } else if (lanes4) {
+    if (rows == 4) rc = launch_scan_r<MODE, 4, 8, 1, true>(st, p, nu);
+    else if (rows == 8) rc = launch_scan_r<MODE, 8, 8, 1, true>(st, p, nu);
+    else if (rows == 16) rc = launch_scan_r<MODE, 16, 8, 1, true>(st, p, nu);
+    else rc = launch_scan_r<MODE, 32, 8, 1, true>(st, p, nu);
   } else {
-    if (p.dim <= 32) rc = launch_scan_r<MODE, 4, 8, 1>(st, p, nu);
-    else if (p.dim <= 64) rc = launch_scan_r<MODE, 8, 8, 1>(st, p, nu);
-    else if (p.dim <= 128) rc = launch_scan_r<MODE, 16, 8, 1>(st, p, nu);
+    if (rows == 4) rc = launch_scan_r<MODE, 4, 8, 1>(st, p, nu);
+    else if (rows == 8) rc = launch_scan_r<MODE, 8, 8, 1>(st, p, nu);
+    else if (rows == 16) rc = launch_scan_r<MODE, 16, 8, 1>(st, p, nu);
     else rc = launch_scan_r<MODE, 32, 8, 1>(st, p, nu);
   }
   B200_TRY(rc);
@@ -638,8 +649,8 @@ int launch_scan(b200_dlm* h, ScanParams p, int n_tok) {
                        run, (long long)u.ntok * H * D, H * (V + 1) * D, (long long)u.ntok * H * V));
     } else {                       // [S_start^T q | n_start . q], then the weighted meeting with the local numerators
       float* corr = h->corr + (long long)u.tok0 * H * (V + 1);
-      B200_TRY(gemm_nt(st, h->scan_prep + (long long)u.tok0 * H * p.prow, H * p.prow, (long long)p.prow, start, D, (V + 1) * D, corr, H * (V + 1), V + 1, u.ntok,
-                       (int)V + 1, (int)D, (int)H, 1.f, 0, run, (long long)u.ntok * H * p.prow, H * (V + 1) * D, (long long)u.ntok * H * (V + 1)));
+      B200_TRY(gemm_nt(st, h->gate32 + (long long)u.tok0 * H * D, H * D, D, start, D, (V + 1) * D, corr, H * (V + 1), V + 1, u.ntok,
+                       (int)V + 1, (int)D, (int)H, 1.f, 0, run, (long long)u.ntok * H * D, H * (V + 1) * D, (long long)u.ntok * H * (V + 1)));
       for (size_t k = i; k < j; ++k) {
         const auto& w = h->units[k];
         const long long rows = (long long)w.ntok * H;
@@ -1082,7 +1093,7 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
       max_qkv = std::max(max_qkv, C);
       max_rv = std::max(max_rv, (size_t)b.heads * b.vdim);
       max_gate = std::max(max_gate, (size_t)b.heads * b.dim);
-      max_prep = std::max(max_prep, (size_t)b.heads * (3 * b.dim + 4));
+      max_prep = std::max(max_prep, (size_t)b.heads * (3 * (size_t)std::max(2 * b.dim, 64) + 4));
       max_segrow = std::max(max_segrow, (size_t)b.heads * (b.vdim + 1) * b.dim);
       max_heads = std::max(max_heads, (size_t)b.heads);
       max_part = std::max(max_part, (size_t)(L.sig_mma >= 0 ? 16 : L.QT) * a.heads * (a.vdim + 2));
@@ -1092,7 +1103,7 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
       B200_TRY(A.alloc_t(&L.mval, (size_t)2 * slots * a.heads));
       max_rv = std::max(max_rv, (size_t)a.heads * a.vdim);
       max_gate = std::max(max_gate, (size_t)2 * a.heads);
-      max_prep = std::max(max_prep, (size_t)a.heads * (2 * a.dim + 8));
+      max_prep = std::max(max_prep, (size_t)a.heads * (2 * (size_t)std::max(2 * a.dim, 64) + 8));
       max_segrow = std::max(max_segrow, (size_t)a.heads * (a.vdim + 1) * a.dim);
       max_heads = std::max(max_heads, (size_t)a.heads);
       max_gate = std::max(max_gate, (size_t)a.heads * a.dim);

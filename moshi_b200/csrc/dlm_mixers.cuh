@@ -574,7 +574,7 @@ struct ScanParams {
   //   segS  [buf][heads][vdim + 1][dim]  the segment's end state (row vdim: mLSTM's n), later replaced by its true start state
   //   segB  [buf][heads][dim]            MODE_DECAY: product of the decays over the segment
   //   segM  [buf][heads][4]              MODE_EXPGATE: sum of the log forget gates, local maximum at the end, (chain: true maximum at the start)
-  //   qb    [tokens][heads * dim]        MODE_DECAY: q times the product of the decays from the segment's start to the token
+  //   qb    [tokens][heads * dim]        q times the product of the decays from the segment's start to the token (MODE_EXPGATE: q)
   //   tokM  [tokens][heads][4]           MODE_EXPGATE: log forget sum so far, local maximum, local n . q
   const int* ent_seg; const int* ent_nseg; const int* ent_buf;
   float *segS, *segB, *segM, *qb, *tokM;
@@ -584,6 +584,7 @@ struct ScanParams {
   const int* ent_pos0;
   float* out;               // [tokens][heads * vdim]
   int heads, dim, vdim, stage, vec;      // vec: rows of prep and the 16-column slices of vprep start on 16 bytes
+  int lpc = 0, rows = 0;    // lane-ordered prep rows for the kernel variant that reads four rows per load (0: plain rows)
 };
 
 // Everything the recurrence reads, as fp32 rows that its CTAs can copy asynchronously: per (token, head)
@@ -594,20 +595,27 @@ template <typename T, int MODE>
 __global__ void __launch_bounds__(256) scan_prep_kernel(ScanParams p) {
   const long long t = blockIdx.x;
   const int heads = p.heads, dim = p.dim;
+  // plain rows (lpc = 0): q, k, a of `dim` elements each.  Lane-ordered rows (lpc > 0, for the recurrence kernel that reads four
+  // rows per load): each padded with zeros to Dp = lpc * rows; lane g of a column owns rows g * rows .. g * rows + rows - 1 and
+  // row g * rows + 4 c + j sits at (c * lpc + g) * 4 + j, so that a quarter-warp's 16-byte loads fall in distinct banks.
+  const int R = p.rows, Dp = p.lpc > 0 ? p.lpc * p.rows : dim;
   const T* row = static_cast<const T*>(p.proj) + t * p.ld;
   float* dst = p.prep + t * heads * p.prow;
-  for (int i = threadIdx.x; i < heads * dim; i += 256) {
-    const int h = i / dim, d = i - h * dim;
+  for (int i = threadIdx.x; i < heads * Dp; i += 256) {
+    const int h = i / Dp, d = i - h * Dp;
+    int at = d;
+    if (p.lpc > 0) { const int g = d / R, w = d - g * R; at = ((w >> 2) * p.lpc + g) * 4 + (w & 3); }
     float* o = dst + h * p.prow;
-    o[d] = to_f(row[p.off_q + i]) * p.qscale;
-    o[dim + d] = to_f(row[p.off_k + i]);
-    if (MODE == MODE_DECAY) o[2 * dim + d] = expf(log_sigmoidf(p.z[t * heads * dim + i] + p.zb[i]) * p.inv_tau);
+    const bool live = d < dim;
+    o[at] = live ? to_f(row[p.off_q + h * dim + d]) * p.qscale : 0.f;
+    o[Dp + at] = live ? to_f(row[p.off_k + h * dim + d]) : 0.f;
+    if (MODE == MODE_DECAY) o[2 * Dp + at] = live ? expf(log_sigmoidf(p.z[t * heads * dim + h * dim + d] + p.zb[h * dim + d]) * p.inv_tau) : 0.f;
   }
   if (MODE == MODE_EXPGATE) {
     for (int i = threadIdx.x; i < 2 * heads; i += 256) {
       const int which = i / heads, h = i - which * heads;
       const float g = p.cap * tanhf(p.z[t * 2 * heads + i] / p.cap);
-      dst[h * p.prow + 2 * dim + which] = which ? log_sigmoidf(g) : g;
+      dst[h * p.prow + 2 * Dp + which] = which ? log_sigmoidf(g) : g;
     }
   }
   for (int i = threadIdx.x; i < heads * p.vdim; i += 256) p.vprep[t * heads * p.vdim + i] = to_f(row[p.off_v + i]);
@@ -628,9 +636,10 @@ __device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* src, 
 // copied asynchronously into one of two shared-memory buffers while the other is being consumed.  mLSTM's n and m exist once
 // per (slot, head) in two generations: every CTA reads generation `par` of its entry, the CTA of the first columns writes
 // generation `par ^ 1`.  Grid: (entries * heads, ceil(vdim / (128 / LPC * CB))).
-template <int MODE, int R, int LPC, int CB>      // R rows per thread (dim <= LPC * R), CB adjacent columns per thread
-__global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
+template <int MODE, int R, int LPC, int CB, bool VL = false>      // R rows per thread (dim <= LPC * R), CB adjacent columns per thread
+__global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {      // VL: a thread's rows are adjacent, read four at a time from lane-ordered prep rows
   constexpr int NC = 128 / LPC * CB;                  // columns per CTA
+  constexpr int Dp = LPC * R;
   const int TT = p.stage;
   extern __shared__ __align__(16) float sm[];
   const int dim = p.dim, vdim = p.vdim, heads = p.heads, prow = p.prow;
@@ -649,7 +658,7 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
   float S[R][CB], nv[R], m = 0.f;
 #pragma unroll
   for (int i = 0; i < R; ++i) {
-    const int r = rg + LPC * i;
+    const int r = VL ? rg * R + i : rg + LPC * i;
     const bool live = pos0 > 0 && seg == 0 && r < dim;
 #pragma unroll
     for (int j = 0; j < CB; ++j) S[i][j] = live && col + j < vdim ? Sbase[(long long)(col + j) * dim + r] : 0.f;
@@ -693,8 +702,8 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
 #pragma unroll 2
     for (int tt = 0; tt < tn; ++tt) {
       const float* qq = base + tt * srow;
-      const float* kk = qq + dim;
-      const float* aa = kk + dim;
+      const float* kk = qq + (VL ? Dp : dim);
+      const float* aa = kk + (VL ? Dp : dim);
       float v[CB], acc[CB], nq = 0.f, fa = 1.f, fb = 1.f, m2 = 0.f;
 #pragma unroll
       for (int j = 0; j < CB; ++j) { v[j] = col + j < vdim ? qq[prow + cl + j] : 0.f; acc[j] = 0.f; }
@@ -706,24 +715,55 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
         m = m2;
         logF += fl;
       }
+      if (VL) {
 #pragma unroll
-      for (int i = 0; i < R; ++i) {
-        const int r = rg + LPC * i;
-        if (r < dim) {
-          const float kv = kk[r] * fb, qv = qq[r];
-          const float ar = MODE == MODE_DECAY ? aa[r] : fa;
-          if (MODE == MODE_DECAY && seg > 0) {
-            bdec[i] *= ar;
-            if (lead) p.qb[(long long)(tok0 + t0 + tt) * heads * dim + head * dim + r] = qv * bdec[i];
+        for (int c4 = 0; c4 < R / 4; ++c4) {         // rows past dim are zeros in q, k and a: they stay zero and add nothing
+          const float4 q4 = *reinterpret_cast<const float4*>(qq + (c4 * LPC + rg) * 4);
+          const float4 k4 = *reinterpret_cast<const float4*>(kk + (c4 * LPC + rg) * 4);
+          const float qv4[4] = {q4.x, q4.y, q4.z, q4.w}, kv4[4] = {k4.x * fb, k4.y * fb, k4.z * fb, k4.w * fb};
+          float av4[4] = {fa, fa, fa, fa};
+          if (MODE == MODE_DECAY) {
+            const float4 a4 = *reinterpret_cast<const float4*>(aa + (c4 * LPC + rg) * 4);
+            av4[0] = a4.x; av4[1] = a4.y; av4[2] = a4.z; av4[3] = a4.w;
           }
 #pragma unroll
-          for (int j = 0; j < CB; ++j) {
-            S[i][j] = fmaf(ar, S[i][j], kv * v[j]);
-            acc[j] = fmaf(S[i][j], qv, acc[j]);
+          for (int w = 0; w < 4; ++w) {
+            const int i = 4 * c4 + w;
+            if (seg > 0) {      // what the carried state is multiplied with: q times the decays so far, or q itself
+              if (MODE == MODE_DECAY) bdec[i] *= av4[w];
+              if (lead && rg * R + i < dim) p.qb[(long long)(tok0 + t0 + tt) * heads * dim + head * dim + rg * R + i] = MODE == MODE_DECAY ? qv4[w] * bdec[i] : qv4[w];
+            }
+#pragma unroll
+            for (int j = 0; j < CB; ++j) {
+              S[i][j] = fmaf(av4[w], S[i][j], kv4[w] * v[j]);
+              acc[j] = fmaf(S[i][j], qv4[w], acc[j]);
+            }
+            if (MODE == MODE_EXPGATE) {
+              nv[i] = fmaf(fa, nv[i], kv4[w]);
+              nq = fmaf(nv[i], qv4[w], nq);
+            }
           }
-          if (MODE == MODE_EXPGATE) {
-            nv[i] = fmaf(fa, nv[i], kv);
-            nq = fmaf(nv[i], qv, nq);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          const int r = rg + LPC * i;
+          if (r < dim) {
+            const float kv = kk[r] * fb, qv = qq[r];
+            const float ar = MODE == MODE_DECAY ? aa[r] : fa;
+            if (seg > 0) {
+              if (MODE == MODE_DECAY) bdec[i] *= ar;
+              if (lead) p.qb[(long long)(tok0 + t0 + tt) * heads * dim + head * dim + r] = MODE == MODE_DECAY ? qv * bdec[i] : qv;
+            }
+#pragma unroll
+            for (int j = 0; j < CB; ++j) {
+              S[i][j] = fmaf(ar, S[i][j], kv * v[j]);
+              acc[j] = fmaf(S[i][j], qv, acc[j]);
+            }
+            if (MODE == MODE_EXPGATE) {
+              nv[i] = fmaf(fa, nv[i], kv);
+              nq = fmaf(nv[i], qv, nq);
+            }
           }
         }
       }
@@ -755,7 +795,7 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
     float* dst = p.segS + sbuf * (vdim + 1) * dim;
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-      const int r = rg + LPC * i;
+      const int r = VL ? rg * R + i : rg + LPC * i;
       if (r < dim) {
 #pragma unroll
         for (int j = 0; j < CB; ++j) if (col + j < vdim) dst[(long long)(col + j) * dim + r] = S[i][j];
@@ -768,7 +808,7 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
   }
 #pragma unroll
   for (int i = 0; i < R; ++i) {
-    const int r = rg + LPC * i;
+    const int r = VL ? rg * R + i : rg + LPC * i;
     if (r < dim) {
 #pragma unroll
       for (int j = 0; j < CB; ++j) if (col + j < vdim) Sbase[(long long)(col + j) * dim + r] = S[i][j];
