@@ -410,7 +410,8 @@ int b200_dlm_set_stream(b200_dlm* h, void* stream);
 /* "use_tc" (before finalize; 1 = bf16 linears of eligible shapes on the LM's tcgen05 GEMM), "trace_layers" (before cache_begin),
  * "attn_split" (CTAs per attention tile along the keys; 0 = chosen per step), "attn_tc" (0: attention and grouped expert
  * products on the CUDA cores also where a tensor-core kernel would take them; 2: the tensor-core window attention also for
- * single-token requests), "time_kernels" (CUDA events around every
+ * single-token requests), "scan_segment" (before cache_begin; tokens per segment of the recurrences: portions of at least two
+ * segments run as segments side by side; default 256), "time_kernels" (CUDA events around every
  * operation, summed per class: a step then waits for its own end). */
 int b200_dlm_set_option(b200_dlm* h, const char* name, int value);
 /* Milliseconds spent so far per class of operation under "time_kernels": [0] linears, [1] attention, [2] the small products
