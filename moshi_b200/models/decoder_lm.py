@@ -1,7 +1,7 @@
 """Text-only decoder LMs given as a list of layers, backed by the sm_100a library (``b200_dlm_*``).
 
-``DecoderLM`` owns the weights (like ``LMModel``); ``DecoderLMGen`` owns the latent cache and runs steps (like ``LMGen`` owns the
-streaming state): a step is a ragged batch, any number of new tokens per cache slot, so prompt portions and single-token
+``DecoderLM`` owns the weights (like ``LMModel``); ``DecoderLMGen`` owns what the cache slots hold (latents, or keys and values,
+carried convolution inputs and recurrent state, by the model's mixers) and runs steps (like ``LMGen`` owns the streaming state): a step is a ragged batch, any number of new tokens per cache slot, so prompt portions and single-token
 decoding are the same call.  Nothing here computes: every operation is a kernel of ``libmoshi_b200.so``.
 """
 from __future__ import annotations
